@@ -1,0 +1,127 @@
+// fp32 SIMT GEMM: C[M,N] = op(A) * op(B), row-major, all four transpose modes, strided-batched.
+//
+// Reference: Gemm::compute_direct / GemmBatched::compute_direct (src/ops/gemm.rs:176-250,
+// 338-421) launch the "XgemmDirect" kernel with 8x8x8 tiles and one output per thread
+// (src/ops/kernels/matmul_direct.opencl:514-709).  This kernel computes the same fp32 products
+// with per-output accumulation in increasing k (each thread walks k = 0..K-1 for its outputs, one
+// fused multiply-add per step), using 128x128x16 tiles and 8x8 outputs per thread.  It serves
+// shapes the tensor-core path cannot take (unaligned leading dimensions, tiny problems) and is
+// the cross-check for that path in the tests.
+#include <cuda_runtime.h>
+
+#include "kernels.h"
+
+namespace sage {
+namespace k {
+
+namespace {
+constexpr int BM = 128, BN = 128, BK = 16;
+
+struct GemmP {
+    long long m, n, k;
+    const float *a;
+    long long lda, sa;
+    const float *b;
+    long long ldb, sb;
+    float *c;
+    long long ldc, sc;
+};
+
+template <bool TA, bool TB>
+__global__ void __launch_bounds__(256) gemm_simt_kernel(GemmP p) {
+    __shared__ __align__(16) float As[BK][BM];
+    __shared__ __align__(16) float Bs[BK][BN];
+    const int t = threadIdx.x;
+    const long long m0 = (long long)blockIdx.y * BM, n0 = (long long)blockIdx.x * BN;
+    const float *A = p.a + (long long)blockIdx.z * p.sa;
+    const float *B = p.b + (long long)blockIdx.z * p.sb;
+    float *C = p.c + (long long)blockIdx.z * p.sc;
+    const int tx = t % 16, ty = t / 16;
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+    for (long long k0 = 0; k0 < p.k; k0 += BK) {
+        // ---- stage A'(i,p) into As[p][i]
+        if (!TA) {
+            const int i = t / 2, pc = (t % 2) * 8;
+            const long long gi = m0 + i;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const long long gp = k0 + pc + q;
+                As[pc + q][i] = (gi < p.m && gp < p.k) ? A[gi * p.lda + gp] : 0.f;
+            }
+        } else {
+            const int pp = t / 16, i0 = (t % 16) * 8;
+            const long long gp = k0 + pp;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const long long gi = m0 + i0 + q;
+                As[pp][i0 + q] = (gi < p.m && gp < p.k) ? A[gp * p.lda + gi] : 0.f;
+            }
+        }
+        // ---- stage B'(p,j) into Bs[p][j]
+        if (!TB) {
+            const int pp = t / 16, j0 = (t % 16) * 8;
+            const long long gp = k0 + pp;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const long long gj = n0 + j0 + q;
+                Bs[pp][j0 + q] = (gj < p.n && gp < p.k) ? B[gp * p.ldb + gj] : 0.f;
+            }
+        } else {
+            const int j = t / 2, pc = (t % 2) * 8;
+            const long long gj = n0 + j;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const long long gp = k0 + pc + q;
+                Bs[pc + q][j] = (gj < p.n && gp < p.k) ? B[gj * p.ldb + gp] : 0.f;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int pp = 0; pp < BK; ++pp) {
+            const float4 a0 = *reinterpret_cast<const float4 *>(&As[pp][ty * 4]);
+            const float4 a1 = *reinterpret_cast<const float4 *>(&As[pp][64 + ty * 4]);
+            const float4 b0 = *reinterpret_cast<const float4 *>(&Bs[pp][tx * 4]);
+            const float4 b1 = *reinterpret_cast<const float4 *>(&Bs[pp][64 + tx * 4]);
+            const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const long long gi = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+        if (gi >= p.m) continue;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const long long gj = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
+            if (gj < p.n) C[gi * p.ldc + gj] = acc[i][j];
+        }
+    }
+}
+}  // namespace
+
+sage_status gemm_simt(Context &ctx, const GemmArgs &g) {
+    ctx.note_launch("gemm_simt");
+    if (ctx.dry() || g.m == 0 || g.n == 0 || g.batch == 0) return SAGE_OK;
+    GemmP p{g.m, g.n, g.k, g.a, g.lda, g.stride_a, g.b, g.ldb, g.stride_b, g.c, g.ldc, g.stride_c};
+    dim3 grid((unsigned)((g.n + BN - 1) / BN), (unsigned)((g.m + BM - 1) / BM), (unsigned)g.batch);
+    if (grid.y > 65535 || grid.z > 65535) return ctx.fail(SAGE_ERR_UNSUPPORTED, "gemm_simt: grid too large");
+    cudaStream_t s = ctx.stream();
+    if (!g.ta && !g.tb) gemm_simt_kernel<false, false><<<grid, 256, 0, s>>>(p);
+    else if (!g.ta && g.tb) gemm_simt_kernel<false, true><<<grid, 256, 0, s>>>(p);
+    else if (g.ta && !g.tb) gemm_simt_kernel<true, false><<<grid, 256, 0, s>>>(p);
+    else gemm_simt_kernel<true, true><<<grid, 256, 0, s>>>(p);
+    return ctx.check_cuda(cudaGetLastError(), "gemm_simt launch");
+}
+
+}  // namespace k
+}  // namespace sage

@@ -1,0 +1,73 @@
+// Host launchers of the hand-written (non-JIT) CUDA kernels.  Pointers are raw device
+// addresses with the tensor's element offset already applied; strides are in elements.
+#pragma once
+#include <cstdint>
+
+#include "../runtime/runtime.h"
+
+namespace sage {
+namespace k {
+
+constexpr int kMaxDims = SAGE_MAX_DIMS;
+
+struct Dims {  // extents + strides of a (sub)space, row-major order of traversal
+    int ndim = 0;
+    long long ext[kMaxDims] = {0};
+    long long str[kMaxDims] = {0};
+    long long size() const {
+        long long p = 1;
+        for (int i = 0; i < ndim; ++i) p *= ext[i];
+        return p;
+    }
+};
+
+// reduce.cu — ReduceOperator / ReduceArgOperator (src/ops/reduce.rs:258-325, 372-431)
+sage_status reduce(Context &ctx, int dtype, int kind, const void *x, const Dims &outer, const Dims &inner, void *y);
+sage_status reduce_arg(Context &ctx, bool is_max, const float *x, const Dims &outer, long long inner_ext,
+                       long long inner_str, uint32_t *y);
+
+// rowops.cu — softmax / log_sum_exp / layer_norm over contiguous rows (src/ops/nn.rs:42-100)
+sage_status softmax_rows(Context &ctx, const float *x, float *y, long long rows, long long cols);
+sage_status lse_rows(Context &ctx, const float *x, float *y, long long rows, long long cols);
+sage_status layernorm_rows(Context &ctx, const float *x, float *y, long long rows, long long cols, const float *gamma,
+                           int gamma_stride, const float *beta, int beta_stride, float eps);
+
+// index.cu — gather / scatter / strided copy (src/ops/core.rs:571-934)
+sage_status gather(Context &ctx, const uint32_t *x, const long long *x_str, const uint32_t *ind, const Dims &ind_dims,
+                   int axis, uint32_t *y);
+sage_status scatter_add(Context &ctx, const float *x, const long long *x_str, const uint32_t *ind, const Dims &ind_dims,
+                        int axis, float *y, const long long *y_str);
+// y[translate(g, dims.ext, y_str)] = x[translate(g, dims.ext, dims.str)]
+sage_status strided_copy(Context &ctx, const uint32_t *x, const Dims &dims, uint32_t *y, const long long *y_str);
+
+// conv.cu — im2col / col2im / direct pooling (src/ops/conv.rs:143-165, 289-498)
+struct Window {
+    int ker_w, ker_h, stride_w, stride_h, pad_w, pad_h, dil_w, dil_h;
+};
+sage_status im2col(Context &ctx, const float *img, float *col, long long n, long long img_h, long long img_w,
+                   long long chan, long long col_h, long long col_w, const Window &w);
+sage_status col2im(Context &ctx, const float *col, float *img, long long n, long long img_h, long long img_w,
+                   long long chan, long long col_h, long long col_w, const Window &w);
+sage_status pool2d(Context &ctx, bool is_max, const float *img, float *out, long long n, long long img_h,
+                   long long img_w, long long chan, long long out_h, long long out_w, const Window &w);
+
+// gemm_simt.cu / gemm_tcgen05.cu — Gemm / GemmBatched (src/ops/gemm.rs:176-250, 338-421)
+struct GemmArgs {
+    bool ta, tb;
+    long long m, n, k;
+    const float *a;
+    long long lda, stride_a;
+    const float *b;
+    long long ldb, stride_b;
+    float *c;
+    long long ldc, stride_c;
+    long long batch;
+};
+sage_status gemm_simt(Context &ctx, const GemmArgs &g);
+// Returns SAGE_ERR_UNSUPPORTED when the shape/alignment cannot go through TMA; the caller
+// then uses gemm_simt.
+sage_status gemm_tcgen05(Context &ctx, const GemmArgs &g);
+sage_status gemm(Context &ctx, const GemmArgs &g);  // picks per ctx.opts().gemm_backend
+
+}  // namespace k
+}  // namespace sage

@@ -1,0 +1,277 @@
+// Reductions: sum / prod / max / min over arbitrary axes, argmax / argmin over one axis.
+//
+// Reference: ReduceOperator::compute (src/ops/reduce.rs:258-325) gives each OUTPUT element to one
+// work-item that loops serially over the reduced axes; a last-axis reduction is then fully
+// uncoalesced.  Here a GROUP of G threads owns one output:
+//   G = 1    adjacent threads own adjacent outputs   -> coalesced when a kept axis is contiguous
+//   G = 32   a warp strides over the reduced run     -> coalesced when a reduced axis is contiguous
+//   G = 256  a whole CTA per output for long runs
+// partial results meet through warp shuffles and a shared-memory tree.
+//
+// Accumulator start: the reference initialises the accumulator to 0 for all four ops
+// (reduce.rs:283), so max returns max(0, ...), min returns min(0, ...) and prod returns 0.  With
+// ref_compat the group result is combined with that 0 once at the end, which is the same value.
+#include <cuda_runtime.h>
+
+#include "kernels.h"
+
+namespace sage {
+namespace k {
+
+struct RDims {
+    int ndim;
+    long long ext[kMaxDims];
+    long long str[kMaxDims];
+};
+
+template <typename T>
+struct Ops {
+    __device__ static T identity(int kind);
+    __device__ static T apply(int kind, T a, T b);
+};
+
+template <>
+struct Ops<float> {
+    __device__ static float identity(int kind) {
+        return kind == 0 ? 0.f : kind == 1 ? 1.f : kind == 2 ? -INFINITY : INFINITY;
+    }
+    __device__ static float apply(int kind, float a, float b) {
+        return kind == 0 ? a + b : kind == 1 ? a * b : kind == 2 ? fmaxf(a, b) : fminf(a, b);
+    }
+};
+template <>
+struct Ops<int> {
+    __device__ static int identity(int kind) { return kind == 0 ? 0 : kind == 1 ? 1 : kind == 2 ? INT_MIN : INT_MAX; }
+    __device__ static int apply(int kind, int a, int b) {
+        return kind == 0 ? a + b : kind == 1 ? a * b : kind == 2 ? max(a, b) : min(a, b);
+    }
+};
+template <>
+struct Ops<unsigned> {
+    __device__ static unsigned identity(int kind) { return kind == 0 ? 0u : kind == 1 ? 1u : kind == 2 ? 0u : UINT_MAX; }
+    __device__ static unsigned apply(int kind, unsigned a, unsigned b) {
+        return kind == 0 ? a + b : kind == 1 ? a * b : kind == 2 ? max(a, b) : min(a, b);
+    }
+};
+
+__device__ __forceinline__ long long translate(long long g, const RDims &d) {
+    long long idx = 0;
+#pragma unroll 1
+    for (int i = d.ndim - 1; i >= 0; --i) {
+        long long c = g % d.ext[i];
+        g /= d.ext[i];
+        idx += c * d.str[i];
+    }
+    return idx;
+}
+
+template <typename T>
+__device__ __forceinline__ T shfl_down_t(T v, int off) {
+    return __shfl_down_sync(0xffffffffu, v, off);
+}
+
+// G threads per output.  blockDim.x is a multiple of G (and of 32).
+template <typename T, int G>
+__global__ void __launch_bounds__(256) reduce_kernel(const T *__restrict__ x, T *__restrict__ y, RDims outer, RDims inner,
+                                                     long long n_out, long long n_in, int kind, int ref_compat) {
+    __shared__ T smem[8];
+    const int groups_per_block = blockDim.x / G;
+    long long out = (long long)blockIdx.x * groups_per_block + threadIdx.x / G;
+    const int lane = threadIdx.x % G;
+    // (For G == 256 every thread of the CTA shares `out`, so the early exit is uniform.)
+    if (out >= n_out) return;
+    const T *base = x + translate(out, outer);
+    T acc = Ops<T>::identity(kind);
+    if (inner.ndim == 1) {
+        const long long s = inner.str[0];
+        long long it = lane;
+        // 4 independent loads in flight per thread
+        T a1 = acc, a2 = acc, a3 = acc;
+        for (; it + 3LL * G < n_in; it += 4LL * G) {
+            T v0 = base[it * s], v1 = base[(it + G) * s], v2 = base[(it + 2LL * G) * s], v3 = base[(it + 3LL * G) * s];
+            acc = Ops<T>::apply(kind, acc, v0);
+            a1 = Ops<T>::apply(kind, a1, v1);
+            a2 = Ops<T>::apply(kind, a2, v2);
+            a3 = Ops<T>::apply(kind, a3, v3);
+        }
+        for (; it < n_in; it += G) acc = Ops<T>::apply(kind, acc, base[it * s]);
+        acc = Ops<T>::apply(kind, Ops<T>::apply(kind, acc, a1), Ops<T>::apply(kind, a2, a3));
+    } else {
+        for (long long it = lane; it < n_in; it += G) acc = Ops<T>::apply(kind, acc, base[translate(it, inner)]);
+    }
+    if (G >= 32) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc = Ops<T>::apply(kind, acc, shfl_down_t(acc, off));
+    }
+    if (G == 256) {
+        const int warp = threadIdx.x >> 5;
+        if ((threadIdx.x & 31) == 0) smem[warp] = acc;
+        __syncthreads();
+        if (threadIdx.x < 8) {
+            acc = smem[threadIdx.x];
+#pragma unroll
+            for (int off = 4; off > 0; off >>= 1) acc = Ops<T>::apply(kind, acc, __shfl_down_sync(0xffu, acc, off));
+        }
+    }
+    if (lane == 0) {
+        if (ref_compat) acc = Ops<T>::apply(kind, (T)0, acc);
+        y[out] = acc;
+    }
+}
+
+// Puts the reduced axis with the smallest non-zero stride last (fastest) and merges axes that
+// form one run, so that a group's lanes read neighbouring addresses.  The order of a parallel
+// reduction is free, so this does not change what is computed.
+static RDims canonical_inner(const Dims &in) {
+    int order[kMaxDims];
+    int n = 0;
+    for (int i = 0; i < in.ndim; ++i)
+        if (in.ext[i] > 1) order[n++] = i;
+    // sort by stride descending
+    for (int i = 0; i < n; ++i)
+        for (int j = i + 1; j < n; ++j)
+            if (in.str[order[j]] > in.str[order[i]]) {
+                int t = order[i];
+                order[i] = order[j];
+                order[j] = t;
+            }
+    RDims r;
+    r.ndim = 0;
+    for (int i = 0; i < n; ++i) {
+        long long e = in.ext[order[i]], s = in.str[order[i]];
+        if (r.ndim > 0 && r.str[r.ndim - 1] == s * e) {
+            r.ext[r.ndim - 1] *= e;
+            r.str[r.ndim - 1] = s;
+        } else {
+            r.ext[r.ndim] = e;
+            r.str[r.ndim] = s;
+            ++r.ndim;
+        }
+    }
+    if (r.ndim == 0) {
+        r.ndim = 1;
+        r.ext[0] = 1;
+        r.str[0] = 0;
+    }
+    return r;
+}
+
+template <typename T>
+static sage_status launch_reduce(Context &ctx, int kind, const T *x, const Dims &outer_in, const Dims &inner_in, T *y) {
+    RDims outer;
+    outer.ndim = outer_in.ndim;
+    for (int i = 0; i < outer_in.ndim; ++i) {
+        outer.ext[i] = outer_in.ext[i];
+        outer.str[i] = outer_in.str[i];
+    }
+    if (outer.ndim == 0) {
+        outer.ndim = 1;
+        outer.ext[0] = 1;
+        outer.str[0] = 0;
+    }
+    RDims inner = canonical_inner(inner_in);
+    long long n_out = outer_in.size(), n_in = 1;
+    for (int i = 0; i < inner.ndim; ++i) n_in *= inner.ext[i];
+    if (n_out == 0) return SAGE_OK;
+    const bool inner_contig = inner.str[inner.ndim - 1] == 1;
+    int G = 1;
+    if (inner_contig && n_in >= 64) G = (n_in >= 8192 || n_out < 2LL * ctx.sm_count) ? 256 : 32;
+    // A column reduction with very few outputs would leave the GPU idle; a CTA per output is
+    // uncoalesced but at least parallel.
+    if (!inner_contig && n_out < 1024 && n_in >= 4096) G = 256;
+    const int threads = 256;
+    long long blocks = (n_out + (threads / G) - 1) / (threads / G);
+    const int compat = ctx.opts().ref_compat;
+    ctx.note_launch(G == 1 ? "reduce_g1" : G == 32 ? "reduce_g32" : "reduce_g256");
+    if (ctx.dry()) return SAGE_OK;
+    if (G == 1)
+        reduce_kernel<T, 1><<<(unsigned)blocks, threads, 0, ctx.stream()>>>(x, y, outer, inner, n_out, n_in, kind, compat);
+    else if (G == 32)
+        reduce_kernel<T, 32><<<(unsigned)blocks, threads, 0, ctx.stream()>>>(x, y, outer, inner, n_out, n_in, kind, compat);
+    else
+        reduce_kernel<T, 256><<<(unsigned)blocks, threads, 0, ctx.stream()>>>(x, y, outer, inner, n_out, n_in, kind, compat);
+    return ctx.check_cuda(cudaGetLastError(), "reduce launch");
+}
+
+sage_status reduce(Context &ctx, int dtype, int kind, const void *x, const Dims &outer, const Dims &inner, void *y) {
+    if (dtype == SAGE_F32) return launch_reduce<float>(ctx, kind, (const float *)x, outer, inner, (float *)y);
+    if (dtype == SAGE_I32) return launch_reduce<int>(ctx, kind, (const int *)x, outer, inner, (int *)y);
+    return launch_reduce<unsigned>(ctx, kind, (const unsigned *)x, outer, inner, (unsigned *)y);
+}
+
+// ---------------------------------------------------------------------------------- argmax / argmin
+// Reference (reduce.rs:396-421): best = x[outer]; for i in 0..extent: if best < x_i (max) or
+// best > x_i (min) { arg = i; best = x_i }.  So the first extremum wins, a NaN never replaces
+// anything, and a NaN at position 0 is never replaced.  The parallel form keeps (value, index)
+// pairs and prefers the smaller index on ties; a NaN at i > 0 is treated as "never wins", and a
+// NaN at 0 pins the answer to 0.  Results are bit-exact with the serial loop.
+__device__ __forceinline__ bool better(bool is_max, float v, unsigned i, float bv, unsigned bi) {
+    if (v != v) return false;    // NaN candidate never wins
+    if (bv != bv) return true;   // placeholder NaN (no candidate yet) loses to anything real
+    if (is_max ? (v > bv) : (v < bv)) return true;
+    return v == bv && i < bi;
+}
+
+template <int G>
+__global__ void __launch_bounds__(256) reduce_arg_kernel(const float *__restrict__ x, unsigned *__restrict__ y, RDims outer,
+                                                         long long n_out, long long n_in, long long stride, int is_max) {
+    long long out = (long long)blockIdx.x * (blockDim.x / G) + threadIdx.x / G;
+    const int lane = threadIdx.x % G;
+    if (out >= n_out) return;
+    const float *base = x + translate(out, outer);
+    float bv = __int_as_float(0x7fc00000);  // "nothing yet"
+    unsigned bi = 0xffffffffu;
+    for (long long it = lane; it < n_in; it += G) {
+        float v = base[it * stride];
+        if (better(is_max, v, (unsigned)it, bv, bi)) {
+            bv = v;
+            bi = (unsigned)it;
+        }
+    }
+    if (G == 32) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            float ov = __shfl_down_sync(0xffffffffu, bv, off);
+            unsigned oi = __shfl_down_sync(0xffffffffu, bi, off);
+            if (oi != 0xffffffffu && better(is_max, ov, oi, bv, bi)) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+    }
+    if (lane == 0) {
+        float first = base[0];
+        // NaN at position 0 is never displaced; no real candidate at all also yields 0.
+        y[out] = (first != first || bi == 0xffffffffu) ? 0u : bi;
+    }
+}
+
+sage_status reduce_arg(Context &ctx, bool is_max, const float *x, const Dims &outer_in, long long inner_ext,
+                       long long inner_str, uint32_t *y) {
+    RDims outer;
+    outer.ndim = outer_in.ndim;
+    for (int i = 0; i < outer_in.ndim; ++i) {
+        outer.ext[i] = outer_in.ext[i];
+        outer.str[i] = outer_in.str[i];
+    }
+    if (outer.ndim == 0) {
+        outer.ndim = 1;
+        outer.ext[0] = 1;
+        outer.str[0] = 0;
+    }
+    long long n_out = outer_in.size();
+    if (n_out == 0) return SAGE_OK;
+    const int G = (inner_str == 1 && inner_ext >= 64) ? 32 : 1;
+    const int threads = 256;
+    long long blocks = (n_out + (threads / G) - 1) / (threads / G);
+    ctx.note_launch(G == 1 ? "reduce_arg_g1" : "reduce_arg_g32");
+    if (ctx.dry()) return SAGE_OK;
+    if (G == 1)
+        reduce_arg_kernel<1><<<(unsigned)blocks, threads, 0, ctx.stream()>>>(x, y, outer, n_out, inner_ext, inner_str, is_max);
+    else
+        reduce_arg_kernel<32><<<(unsigned)blocks, threads, 0, ctx.stream()>>>(x, y, outer, n_out, inner_ext, inner_str, is_max);
+    return ctx.check_cuda(cudaGetLastError(), "reduce_arg launch");
+}
+
+}  // namespace k
+}  // namespace sage

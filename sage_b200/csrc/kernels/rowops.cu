@@ -1,0 +1,215 @@
+// softmax / log_sum_exp / layer_norm over contiguous rows, one kernel each.
+//
+// The reference builds these from 4-7 separate kernels with a DRAM round trip between each
+// (src/ops/nn.rs:42-100 over src/ops/reduce.rs:59-82).  The arithmetic below is the same
+// composition, evaluated per row with the row held in registers:
+//   softmax     m = max_j x_j ; e_j = exp(x_j - m) ; y_j = e_j / sum_j e_j
+//   log_sum_exp c = max_j x_j ; y = log(sum_j exp(x_j - c)) + c
+//   layer_norm  mean = sum(x)/C ; var = sum(x^2)/C - mean^2 ; y = (x-mean)/sqrt(var+eps)*gamma + beta
+// With ref_compat the two max reductions start from 0 like the reference's accumulator
+// (reduce.rs:283), i.e. m = max(0, max_j x_j).
+//
+// A warp owns a row when it fits in registers (cols <= 2048, cols % 4 == 0): lanes read float4
+// chunks `lane + 32*i`, so each pass over HBM is one coalesced read and one coalesced write.
+// Other shapes use a CTA per row that re-reads the row (L2-resident) per pass.
+#include <cuda_runtime.h>
+
+#include "kernels.h"
+
+namespace sage {
+namespace k {
+
+enum { ROW_SOFTMAX = 0, ROW_LSE = 1, ROW_LN = 2 };
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+    return v;
+}
+
+struct RowParams {
+    const float *x;
+    float *y;
+    long long rows, cols;
+    const float *gamma, *beta;
+    int gamma_stride, beta_stride;
+    float eps;
+    int ref_compat;
+};
+
+// V = float4 chunks per lane; the row has cols/4 <= 32*V chunks.
+template <int MODE, int V>
+__global__ void __launch_bounds__(256) row_warp_kernel(RowParams p) {
+    const int lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= p.rows) return;
+    const int chunks = (int)(p.cols >> 2);
+    const float4 *xr = reinterpret_cast<const float4 *>(p.x + row * p.cols);
+    float4 v[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const int c = lane + 32 * i;
+        if (c < chunks) v[i] = __ldg(xr + c);
+    }
+    if (MODE == ROW_LN) {
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+            if (lane + 32 * i < chunks) {
+                s1 += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+                s2 += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+            }
+        s1 = warp_sum(s1);
+        s2 = warp_sum(s2);
+        const float n = (float)p.cols;
+        const float mean = s1 / n;
+        const float var = s2 / n - mean * mean;
+        const float denom = sqrtf(var + p.eps);
+        float4 *yr = reinterpret_cast<float4 *>(p.y + row * p.cols);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const int c = lane + 32 * i;
+            if (c < chunks) {
+                const int e = c * 4;
+                float4 o;
+                o.x = (v[i].x - mean) / denom * p.gamma[(e + 0) * p.gamma_stride] + p.beta[(e + 0) * p.beta_stride];
+                o.y = (v[i].y - mean) / denom * p.gamma[(e + 1) * p.gamma_stride] + p.beta[(e + 1) * p.beta_stride];
+                o.z = (v[i].z - mean) / denom * p.gamma[(e + 2) * p.gamma_stride] + p.beta[(e + 2) * p.beta_stride];
+                o.w = (v[i].w - mean) / denom * p.gamma[(e + 3) * p.gamma_stride] + p.beta[(e + 3) * p.beta_stride];
+                yr[c] = o;
+            }
+        }
+        return;
+    }
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < V; ++i)
+        if (lane + 32 * i < chunks) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+    m = warp_max(m);
+    if (p.ref_compat) m = fmaxf(0.f, m);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < V; ++i)
+        if (lane + 32 * i < chunks) {
+            v[i].x = expf(v[i].x - m);
+            v[i].y = expf(v[i].y - m);
+            v[i].z = expf(v[i].z - m);
+            v[i].w = expf(v[i].w - m);
+            s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        }
+    s = warp_sum(s);
+    if (MODE == ROW_LSE) {
+        if (lane == 0) p.y[row] = logf(s) + m;
+        return;
+    }
+    float4 *yr = reinterpret_cast<float4 *>(p.y + row * p.cols);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const int c = lane + 32 * i;
+        if (c < chunks) {
+            float4 o;
+            o.x = v[i].x / s;
+            o.y = v[i].y / s;
+            o.z = v[i].z / s;
+            o.w = v[i].w / s;
+            yr[c] = o;
+        }
+    }
+}
+
+__device__ __forceinline__ float block_reduce(float v, bool is_max, float *smem) {
+    v = is_max ? warp_max(v) : warp_sum(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();  // smem may still be read from a previous call
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    const int nw = blockDim.x >> 5;
+    float r = lane < nw ? smem[lane] : (is_max ? -INFINITY : 0.f);
+    r = is_max ? warp_max(r) : warp_sum(r);
+    return r;
+}
+
+// Any row length: one CTA per row, the row is re-read per pass.
+template <int MODE>
+__global__ void __launch_bounds__(256) row_block_kernel(RowParams p) {
+    __shared__ float smem[8];
+    const long long row = blockIdx.x;
+    const float *xr = p.x + row * p.cols;
+    float *yr = p.y + row * p.cols;
+    if (MODE == ROW_LN) {
+        float s1 = 0.f, s2 = 0.f;
+        for (long long j = threadIdx.x; j < p.cols; j += blockDim.x) {
+            float v = xr[j];
+            s1 += v;
+            s2 += v * v;
+        }
+        s1 = block_reduce(s1, false, smem);
+        s2 = block_reduce(s2, false, smem);
+        const float n = (float)p.cols;
+        const float mean = s1 / n;
+        const float var = s2 / n - mean * mean;
+        const float denom = sqrtf(var + p.eps);
+        for (long long j = threadIdx.x; j < p.cols; j += blockDim.x)
+            yr[j] = (xr[j] - mean) / denom * p.gamma[j * p.gamma_stride] + p.beta[j * p.beta_stride];
+        return;
+    }
+    float m = -INFINITY;
+    for (long long j = threadIdx.x; j < p.cols; j += blockDim.x) m = fmaxf(m, xr[j]);
+    m = block_reduce(m, true, smem);
+    if (p.ref_compat) m = fmaxf(0.f, m);
+    float s = 0.f;
+    for (long long j = threadIdx.x; j < p.cols; j += blockDim.x) s += expf(xr[j] - m);
+    s = block_reduce(s, false, smem);
+    if (MODE == ROW_LSE) {
+        if (threadIdx.x == 0) p.y[row] = logf(s) + m;
+        return;
+    }
+    for (long long j = threadIdx.x; j < p.cols; j += blockDim.x) yr[j] = expf(xr[j] - m) / s;
+}
+
+template <int MODE>
+static sage_status launch_rows(Context &ctx, RowParams p, const char *name) {
+    ctx.note_launch(name);
+    if (ctx.dry() || p.rows == 0) return SAGE_OK;
+    p.ref_compat = ctx.opts().ref_compat;
+    const bool aligned = (reinterpret_cast<uintptr_t>(p.x) % 16 == 0) &&
+                         (MODE == ROW_LSE || reinterpret_cast<uintptr_t>(p.y) % 16 == 0);
+    if (p.cols % 4 == 0 && p.cols <= 2048 && aligned) {
+        const int chunks = (int)(p.cols / 4);
+        const int v = (chunks + 31) / 32;
+        const unsigned blocks = (unsigned)((p.rows + 7) / 8);
+        cudaStream_t s = ctx.stream();
+        if (v <= 1) row_warp_kernel<MODE, 1><<<blocks, 256, 0, s>>>(p);
+        else if (v <= 2) row_warp_kernel<MODE, 2><<<blocks, 256, 0, s>>>(p);
+        else if (v <= 4) row_warp_kernel<MODE, 4><<<blocks, 256, 0, s>>>(p);
+        else if (v <= 8) row_warp_kernel<MODE, 8><<<blocks, 256, 0, s>>>(p);
+        else row_warp_kernel<MODE, 16><<<blocks, 256, 0, s>>>(p);
+    } else {
+        row_block_kernel<MODE><<<(unsigned)p.rows, 256, 0, ctx.stream()>>>(p);
+    }
+    return ctx.check_cuda(cudaGetLastError(), name);
+}
+
+sage_status softmax_rows(Context &ctx, const float *x, float *y, long long rows, long long cols) {
+    RowParams p{x, y, rows, cols, nullptr, nullptr, 0, 0, 0.f, 1};
+    return launch_rows<ROW_SOFTMAX>(ctx, p, "softmax_rows");
+}
+
+sage_status lse_rows(Context &ctx, const float *x, float *y, long long rows, long long cols) {
+    RowParams p{x, y, rows, cols, nullptr, nullptr, 0, 0, 0.f, 1};
+    return launch_rows<ROW_LSE>(ctx, p, "lse_rows");
+}
+
+sage_status layernorm_rows(Context &ctx, const float *x, float *y, long long rows, long long cols, const float *gamma,
+                           int gamma_stride, const float *beta, int beta_stride, float eps) {
+    RowParams p{x, y, rows, cols, gamma, beta, gamma_stride, beta_stride, eps, 1};
+    return launch_rows<ROW_LN>(ctx, p, "layernorm_rows");
+}
+
+}  // namespace k
+}  // namespace sage

@@ -1,0 +1,452 @@
+"""GPU parity: the CUDA path (through the C ABI of libsagecuda.so) against the CPU oracle on the
+same seeded inputs, and against the reference's golden vectors.
+
+Tolerances (from the task's north star): gather / scatter(unique) / argmax / integer casts are
+bit-exact; f32 results have max relative error <= 1e-4 measured as
+|a - b| / max(|b|, 1e-6 * max|b|)  for elementwise work, and for contractions (whose outputs can
+cancel to ~0, where any two fp32 summation orders differ by more than 1e-4 of the value)
+|a - b| / max(|b|, 1e-3 * max|b|);  full model logits <= 1e-3.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import sage_b200 as S
+from oracle import sage_ref as R
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+with open(os.path.join(HERE, "golden", "reference_vectors.json")) as f:
+    GOLD = json.load(f)
+
+
+def vec(test, name, nth=0, dtype=np.float32):
+    hits = [v["value"] for v in GOLD[test]["vectors"] if v["name"] == name]
+    return np.array(hits[nth], dtype=dtype)
+
+
+def rel_err(a, b, floor=1e-6):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    assert a.shape == b.shape, (a.shape, b.shape)
+    if a.size == 0:
+        return 0.0
+    scale = np.maximum(np.abs(b), floor * max(np.abs(b).max(), 1e-30))
+    return float((np.abs(a - b) / scale).max())
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = S.Context(0)
+    yield c
+    c.close()
+
+
+def RV(a, dtype=None):
+    return R.Var.new(R.Tensor.new(a, dtype))
+
+
+# ------------------------------------------------------------------------------ golden vectors on the GPU
+def test_golden_maps(ctx):  # src/ops/map.rs:1383-1676
+    close = lambda y, gt, eps: np.testing.assert_allclose(y, gt, atol=eps, rtol=0)
+    close(S.scalar(3.0, [3, 3]).eval(ctx), vec("map.test_nullary_map", "y_gt"), 1e-3)
+    x, y = vec("map.test_unary_map", "x"), vec("map.test_unary_map", "y_gt")
+    xv = ctx.var(x)
+    close(S.sin(xv).eval(ctx), y, 1e-3)
+    close(S.sin(xv.transpose(0, 1)).eval(ctx), y.transpose(1, 0, 2), 1e-3)
+    x1, x2, y = (vec("map.test_binary_map", n) for n in ("x1", "x2", "y_gt"))
+    a, b = ctx.var(x1), ctx.var(x2)
+    close(S.sub(a, b).eval(ctx), y, 1e-3)
+    close(S.sub(a.tr(), b.tr()).eval(ctx), y.T, 1e-3)
+    x1, x2, y = (vec("map.test_ternary_map", n) for n in ("x1", "x2", "y_gt"))
+    a, b = ctx.var(x1), ctx.var(x2)
+    close(S.cond(S.gt(a, 0.0), a, b).eval(ctx), y, 1e-3)
+    x1, x2, x3, y = (vec("map.test_variadic_map", n) for n in ("x1", "x2", "x3", "y_gt"))
+    a, b, c = ctx.var(x1), ctx.var(x2), ctx.var(x3)
+    close((((a + b * 3.0) - c / 2.0) / b).eval(ctx), y, 1e-2)
+
+
+def test_golden_core(ctx):  # src/ops/core.rs:946-1233
+    close = lambda y, gt: np.testing.assert_allclose(y, gt, atol=1e-3, rtol=0)
+    a = ctx.var(vec("core.test_reshape", "a"))
+    b = a.view([4, 2, 3])
+    close(b.eval(ctx), vec("core.test_reshape", "b_gt"))
+    close(b.transpose(0, 1).view([4, 2, 3]).eval(ctx), vec("core.test_reshape", "c_gt"))
+    close(S.expand(ctx.var(vec("core.test_expand", "x")), [3, 4]).organize().eval(ctx), vec("core.test_expand", "y_gt"))
+    close(S.permute(ctx.var(vec("core.test_permute", "x")), [2, 3, 4, 1, 0]).organize().eval(ctx), vec("core.test_permute", "y_gt"))
+    close(S.slice_(ctx.var(vec("core.test_slice", "x")), 1, 1, 2).organize().eval(ctx), vec("core.test_slice", "y_gt"))
+    close(S.unslice(ctx.var(vec("core.test_unslice", "x")), 1, 1, 3).eval(ctx), vec("core.test_unslice", "y_gt"))
+    t = ctx.var(vec("core.test_gather", "t", dtype=np.uint32))
+    close(S.gather(ctx.var(vec("core.test_gather", "x")), t, 2).eval(ctx), vec("core.test_gather", "y_gt"))
+    xs = [ctx.var(vec("core.test_concat", n)) for n in ("x1", "x2", "x3")]
+    close(S.concat(xs, 1).eval(ctx), vec("core.test_concat", "y_gt"))
+
+
+def test_golden_reduce_gemm_conv_nn(ctx):
+    close = lambda y, gt, eps=1e-3: np.testing.assert_allclose(y, gt, atol=eps, rtol=0)
+    close(S.mean(ctx.var(vec("reduce.test_reduce", "x")), [0, 2, 3], False).eval(ctx), vec("reduce.test_reduce", "y_gt"))
+    y = S.argmax(ctx.var(vec("reduce.test_reduce_arg", "x")), 1, False).eval(ctx)
+    assert y.dtype == np.uint32 and np.array_equal(y, vec("reduce.test_reduce_arg", "y_gt", dtype=np.uint32))
+    a, b = ctx.var(vec("gemm.test_gemm", "a", 0)), ctx.var(vec("gemm.test_gemm", "b", 0))
+    close(S.gemm(a, b).eval(ctx), vec("gemm.test_gemm", "c_gt"))
+    a, b = ctx.var(vec("gemm.test_gemm", "a", 1)), ctx.var(vec("gemm.test_gemm", "b", 1))
+    for name, ta, tb in (("cff_gt", 0, 0), ("ctf_gt", 1, 0), ("cft_gt", 0, 1), ("ctt_gt", 1, 1)):
+        close(S.gemm(a, b, ta, tb).eval(ctx), vec("gemm.test_gemm", name))
+    close(S.im2col(ctx.var(vec("conv.test_im2col", "x")), [3, 2], [1, 1], [0, 0], [1, 1]).eval(ctx), vec("conv.test_im2col", "y_gt"))
+    close(S.col2im(ctx.var(vec("conv.test_col2im", "x")), [4, 5], [3, 2], [1, 1], [0, 0], [1, 1]).eval(ctx), vec("conv.test_col2im", "y_gt"))
+    x, f = ctx.var(vec("conv.test_conv2d", "x")), ctx.var(vec("conv.test_conv2d", "filter"))
+    close(S.conv_2d(x, f, [1, 1], [1, 1], [1, 1]).eval(ctx), vec("conv.test_conv2d", "y_gt"))
+    close(S.relu(ctx.var(vec("nn.test_relu", "x"))).eval(ctx), vec("nn.test_relu", "y_gt"))
+    close(S.softmax(ctx.var(vec("nn.test_softmax", "x")), 1).eval(ctx), vec("nn.test_softmax", "y_gt"))
+    x = ctx.var(vec("nn.test_softmax_cross_entropy", "x"))
+    lab = ctx.var(vec("nn.test_softmax_cross_entropy", "label", dtype=np.uint32))
+    loss = S.softmax_cross_entropy(x, lab)
+    close(loss.eval(ctx), vec("nn.test_softmax_cross_entropy", "loss_gt"))
+    close(x.grad(loss).eval(ctx) / np.float32(5), vec("nn.test_softmax_cross_entropy", "gx_gt"))
+    close(S.max_pool_2d(ctx.var(vec("nn.test_max_pool_2d", "x")), 3, 1, 0, 1).eval(ctx), vec("nn.test_max_pool_2d", "y_gt"), 1e-2)
+
+
+# ------------------------------------------------------------------------------ maps vs oracle
+UNARY = ["abs", "neg", "recip", "log", "exp", "sqrt", "square", "erf", "sign", "ceil", "floor", "round", "sin", "sinh", "cos",
+         "cosh", "tan", "tanh", "asin", "asinh", "acos", "acosh", "atan", "atanh"]
+
+
+@pytest.mark.parametrize("name", UNARY)
+def test_unary_vs_oracle(ctx, name):
+    rng = np.random.default_rng(7)
+    x = rng.uniform(-3, 3, (37, 129)).astype(np.float32)
+    if name in ("log", "sqrt"):
+        x = np.abs(x) + np.float32(0.01)
+    if name in ("asin", "acos", "atanh"):
+        x = (x / 3.5).astype(np.float32)
+    if name == "acosh":
+        x = np.abs(x) + np.float32(1.01)
+    if name in ("ceil", "floor", "round", "sign"):
+        x[0, :5] = [0.5, -0.5, 1.5, -2.5, 0.0]
+    ref = getattr(R, name + "_" if name in ("abs", "round") else name)(RV(x)).eval().numpy()
+    got = getattr(ctx.var(x), name)().eval(ctx)
+    if name in ("ceil", "floor", "round", "sign", "abs", "neg"):
+        assert np.array_equal(got, ref)
+    else:
+        assert rel_err(got, ref) <= 1e-4
+
+
+def test_binary_logic_casts_exact(ctx):
+    rng = np.random.default_rng(8)
+    a = rng.integers(-5, 5, (33, 65)).astype(np.float32)
+    b = rng.integers(-5, 5, (33, 65)).astype(np.float32)
+    va, vb = ctx.var(a), ctx.var(b)
+    for name in ("eq", "ne", "gt", "ge", "lt", "le", "minimum", "maximum", "add", "sub", "mul"):
+        got = getattr(S, name)(va, vb).eval(ctx)
+        ref = getattr(R, name)(RV(a), RV(b)).eval().numpy()
+        assert got.dtype == ref.dtype and np.array_equal(got, ref), name
+    x = rng.uniform(-100, 100, (1000,)).astype(np.float32)
+    gi = ctx.var(x).int().eval(ctx)
+    assert gi.dtype == np.int32 and np.array_equal(gi, np.trunc(x).astype(np.int32))  # (int)x truncates toward zero
+    u = rng.integers(0, 2, (1000,)).astype(np.uint32)
+    gf = ctx.var(u).float().eval(ctx)
+    assert gf.dtype == np.float32 and np.array_equal(gf, u.astype(np.float32))
+
+
+def test_broadcast_and_strided_views(ctx):
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((6, 5, 8)).astype(np.float32)
+    bias = rng.standard_normal((8,)).astype(np.float32)
+    col = rng.standard_normal((6, 1, 1)).astype(np.float32)
+    got = ((ctx.var(x) + ctx.var(bias)) * ctx.var(col)).eval(ctx)
+    ref = ((RV(x) + RV(bias)) * RV(col)).eval().numpy()
+    assert rel_err(got, ref) <= 1e-4
+    # transposed + sliced inputs: generic strided index path
+    xv = ctx.var(x)
+    got = (xv.transpose(0, 2).slice(1, 1, 4) * 2.0).eval(ctx)
+    ref = (R.slice_(R.transpose(RV(x), 0, 2), 1, 1, 4) * 2.0).eval().numpy()
+    assert np.array_equal(got, ref)
+    # ragged (not a multiple of 4) and tiny sizes
+    for n in (1, 3, 5, 1023):
+        v = rng.standard_normal((n,)).astype(np.float32)
+        assert np.array_equal((ctx.var(v) * 2.0 + 1.0).eval(ctx), (RV(v) * 2.0 + 1.0).eval().numpy()) or \
+            rel_err((ctx.var(v) * 2.0 + 1.0).eval(ctx), (RV(v) * 2.0 + 1.0).eval().numpy()) <= 1e-6
+
+
+# ------------------------------------------------------------------------------ reductions
+@pytest.mark.parametrize("shape,axes,preserve", [
+    ((64, 1000), [1], True), ((64, 1000), [0], False), ((7, 9, 11, 5), [0, 2], False), ((7, 9, 11, 5), [3, 1], True),
+    ((3, 20000), [1], False), ((5000, 3), [0], False), ((2, 3, 4), [0, 1, 2], False), ((1, 1), [1], True)])
+@pytest.mark.parametrize("kind", ["sum", "max", "min", "prod"])
+def test_reduce_vs_oracle(ctx, shape, axes, preserve, kind):
+    rng = np.random.default_rng(10)
+    x = rng.uniform(-1.5, 1.5, shape).astype(np.float32)
+    if kind == "prod":
+        x = rng.uniform(0.9, 1.1, shape).astype(np.float32)
+    got = getattr(ctx.var(x), kind)(axes, preserve).eval(ctx)
+    ref = R.reduce(RV(x), axes, preserve, kind).eval().numpy()
+    if kind in ("max", "min", "prod"):  # prod is identically 0 in the reference (accumulator starts at 0)
+        assert np.array_equal(got, ref)
+    else:
+        n_red = int(np.prod([shape[a] for a in axes]))
+        # a sum of n terms in a different order: bounded by n * eps * sum|x|; compare against that scale
+        scale = np.abs(x).sum(axis=tuple(axes), keepdims=preserve).reshape(ref.shape)
+        assert np.all(np.abs(got.astype(np.float64) - ref) <= 1e-6 * np.maximum(scale, 1e-30) * max(1, np.log2(n_red)))
+
+
+def test_reduce_int_exact_and_true_identities():
+    c = S.Context(0, ref_compat=0)
+    try:
+        x = np.random.default_rng(11).integers(-50, 50, (17, 33)).astype(np.int32)
+        assert np.array_equal(c.var(x).sum([1]).eval(c), x.sum(axis=1, dtype=np.int32))
+        assert np.array_equal(c.var(x).max([0]).eval(c), x.max(axis=0))
+        f = -np.abs(np.random.default_rng(12).standard_normal((5, 9))).astype(np.float32)
+        assert np.array_equal(c.var(f).max([1]).eval(c), f.max(axis=1))  # with true identities max of negatives is negative
+    finally:
+        c.close()
+
+
+def test_argmax_argmin_exact(ctx):
+    rng = np.random.default_rng(13)
+    for shape, axis in (((40, 300), 1), ((300, 40), 0), ((6, 7, 8), 1), ((3, 5000), 1)):
+        x = rng.integers(-3, 3, shape).astype(np.float32)  # many ties: first extremum must win
+        x.flat[::17] = np.nan
+        for fn, rfn in ((S.argmax, R.argmax), (S.argmin, R.argmin)):
+            got = fn(ctx.var(x), axis, False).eval(ctx)
+            ref = rfn(RV(x), axis, False).eval().numpy()
+            assert got.dtype == np.uint32 and np.array_equal(got, ref)
+
+
+# ------------------------------------------------------------------------------ gather / scatter
+def test_gather_scatter_exact(ctx):
+    rng = np.random.default_rng(14)
+    x = rng.standard_normal((50, 64)).astype(np.float32)
+    idx = rng.integers(0, 64, (50, 1)).astype(np.uint32)
+    got = S.gather(ctx.var(x), ctx.var(idx), 1).eval(ctx)
+    assert np.array_equal(got, R.gather(RV(x), RV(idx, R.UINT), 1).eval().numpy())
+    # embedding-style: stride-0 expanded index along the last axis (src/layers.rs:438-446)
+    w = rng.standard_normal((100, 24)).astype(np.float32)
+    ids = rng.integers(0, 100, (33,)).astype(np.uint32)
+    iv = S.expand(ctx.var(ids).view([33, 1]), [33, 24])
+    got = S.gather(ctx.var(w), iv, 0).eval(ctx)
+    assert np.array_equal(got, w[ids])
+    # scatter with unique indices is bit-exact with the reference's read-modify-write
+    g = rng.standard_normal((50, 1)).astype(np.float32)
+    got = S.scatter(ctx.var(g), ctx.var(idx), 1, [50, 64]).eval(ctx)
+    ref = R.scatter(RV(g), RV(idx, R.UINT), 1, [50, 64]).eval().numpy()
+    assert np.array_equal(got, ref)
+
+
+# ------------------------------------------------------------------------------ composites
+@pytest.mark.parametrize("shape", [(64, 128), (33, 768), (5, 1000), (7, 130), (3, 5000), (2, 3, 16, 16)])
+def test_softmax_lse_layernorm_vs_oracle(ctx, shape):
+    rng = np.random.default_rng(15)
+    x = (rng.standard_normal(shape) * 3).astype(np.float32)
+    ax = len(shape) - 1
+    assert rel_err(S.softmax(ctx.var(x), [ax]).eval(ctx), R.softmax(RV(x), [ax]).eval().numpy()) <= 1e-4
+    assert rel_err(S.log_sum_exp(ctx.var(x), [ax]).eval(ctx), R.log_sum_exp(RV(x), [ax]).eval().numpy()) <= 1e-4
+    g, b = np.float32([1.3]), np.float32([-0.2])
+    got = S.layer_norm(ctx.var(x), [ax], ctx.var(g), ctx.var(b), 1e-5).eval(ctx)
+    ref = R.layer_norm(RV(x), [ax], RV(g), RV(b), 1e-5).eval().numpy()
+    assert rel_err(got, ref, floor=1e-4) <= 1e-4
+
+
+def test_fused_and_unfused_composites_agree():
+    rng = np.random.default_rng(16)
+    x = rng.standard_normal((40, 96)).astype(np.float32)
+    outs = []
+    for fusion in (1, 0):
+        c = S.Context(0, pattern_fusion=fusion)
+        try:
+            v = c.var(x)
+            g, b = c.var(np.float32([1.0])), c.var(np.float32([0.5]))
+            outs.append((S.softmax(v, [1]).eval(c), S.layer_norm(v, [1], g, b, 1e-5).eval(c), S.log_sum_exp(v, [1]).eval(c)))
+        finally:
+            c.close()
+    for a, b in zip(*outs):
+        assert rel_err(a, b, floor=1e-4) <= 1e-4
+
+
+# ------------------------------------------------------------------------------ config 1 (BASELINE): fused map + reduce graph
+def config1(n, c, seed=1001):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((n, c), dtype=np.float32)
+    y = rng.standard_normal((n, c), dtype=np.float32)
+    labels = rng.integers(0, c, (n, 1)).astype(np.uint32)
+    return x, y, labels
+
+
+def test_config1_forward_and_grad(ctx):
+    x, y, labels = config1(1024, 1024)
+    xv, yv, lv = ctx.var(x), ctx.var(y), ctx.var(labels)
+    loss = S.softmax_cross_entropy(xv * yv + xv * 3.14, lv)
+    gx = xv.grad(loss)
+    ctx.eval(loss, gx)
+    rx, ry, rl = RV(x), RV(y), RV(labels, R.UINT)
+    rloss = R.softmax_cross_entropy(rx * ry + rx * 3.14, rl)
+    rgx = rx.grad(rloss)
+    ref_loss, ref_gx = [t.numpy() for t in R.evaluate([rloss, rgx])]
+    assert rel_err(ctx.read(loss), ref_loss) <= 1e-4
+    assert rel_err(ctx.read(gx), ref_gx, floor=1e-5) <= 1e-4
+
+
+# ------------------------------------------------------------------------------ config 2: contractions
+def gemm_err(got, ref):
+    return rel_err(got, ref, floor=1e-3)
+
+
+@pytest.mark.parametrize("m,n,k", [(1024, 1024, 1024), (1, 1, 1), (7, 13, 5), (129, 257, 63), (128, 768, 3072), (300, 2, 768)])
+def test_matmul_vs_oracle(ctx, m, n, k):
+    rng = np.random.default_rng(2001)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    got = S.matmul(ctx.var(a), ctx.var(b)).eval(ctx)
+    ref = R.matmul(RV(a), RV(b)).eval().numpy()
+    assert gemm_err(got, ref) <= 1e-4
+    f64 = a.astype(np.float64) @ b.astype(np.float64)
+    assert np.linalg.norm(got - f64) / max(np.linalg.norm(f64), 1e-30) <= 2e-6
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_gemm_transposes_vs_oracle(ctx, ta, tb):
+    rng = np.random.default_rng(2002)
+    m, n, k = 200, 136, 72
+    a = rng.uniform(-1, 1, (k, m) if ta else (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (n, k) if tb else (k, n)).astype(np.float32)
+    got = S.gemm(ctx.var(a), ctx.var(b), ta, tb).eval(ctx)
+    ref = R.gemm(RV(a), RV(b), bool(ta), bool(tb)).eval().numpy()
+    assert gemm_err(got, ref) <= 1e-4
+
+
+@pytest.mark.parametrize("sa,sb", [((16, 512, 64), (16, 64, 512)), ((16, 512, 512), (16, 512, 64)), ((3, 5, 7), (3, 7, 2))])
+def test_batch_matmul_vs_oracle(ctx, sa, sb):
+    rng = np.random.default_rng(2003)
+    a = rng.uniform(-1, 1, sa).astype(np.float32)
+    b = rng.uniform(-1, 1, sb).astype(np.float32)
+    got = S.matmul_batched(ctx.var(a), ctx.var(b)).eval(ctx)
+    ref = R.matmul_batched(RV(a), RV(b)).eval().numpy()
+    assert gemm_err(got, ref) <= 1e-4
+
+
+@pytest.mark.parametrize("n", [4096, 8192])
+def test_matmul_large_properties(ctx, n):
+    """At the full BASELINE sizes the oracle is too slow; use size-independent properties:
+    sampled rows against float64, and linearity A(B1 + B2) = A B1 + A B2."""
+    rng = np.random.default_rng(2004 + n)
+    a = rng.uniform(-1, 1, (n, n)).astype(np.float32)
+    b = rng.uniform(-1, 1, (n, n)).astype(np.float32)
+    va, vb = ctx.var(a), ctx.var(b)
+    got = S.matmul(va, vb).eval(ctx)
+    rows = rng.integers(0, n, 16)
+    f64 = a[rows].astype(np.float64) @ b.astype(np.float64)
+    assert gemm_err(got[rows], f64) <= 1e-4
+    b2 = rng.uniform(-1, 1, (n, n)).astype(np.float32)
+    vb2 = ctx.var(b2)
+    lhs = S.matmul(va, vb + vb2).eval(ctx)
+    rhs = got + S.matmul(va, vb2).eval(ctx)
+    assert np.linalg.norm(lhs - rhs) / np.linalg.norm(rhs) <= 1e-5
+
+
+# ------------------------------------------------------------------------------ conv / pooling
+def test_conv_pool_vs_oracle(ctx):
+    rng = np.random.default_rng(5001)
+    x = rng.standard_normal((3, 17, 19, 5)).astype(np.float32)
+    f = (rng.standard_normal((3, 3, 5, 8)) * 0.2).astype(np.float32)
+    for stride, pad in ((1, 1), (2, 1), (2, 0)):
+        got = S.conv_2d(ctx.var(x), ctx.var(f), stride, pad, 1).eval(ctx)
+        ref = R.conv_2d(RV(x), RV(f), stride, pad, 1).eval().numpy()
+        assert gemm_err(got, ref) <= 1e-4
+    got = S.max_pool_2d(ctx.var(x), 3, 2, 1, 1).eval(ctx)
+    assert np.array_equal(got, R.max_pool_2d(RV(x), 3, 2, 1, 1).eval().numpy())
+    got = S.avg_pool_2d(ctx.var(x), [19, 17], [19, 17], 0, 1).eval(ctx)
+    assert rel_err(got, R.avg_pool_2d(RV(x), [19, 17], [19, 17], 0, 1).eval().numpy(), floor=1e-3) <= 1e-4
+
+
+# ------------------------------------------------------------------------------ models
+def init_params(rng, shapes, std=0.02):
+    return [(rng.standard_normal(s) * std).astype(np.float32) for s in shapes]
+
+
+def run_bert(ctx, cfg, batch, seq, seed, pad=False, **ref_kw):
+    rng = np.random.default_rng(seed)
+    model = S.Bert(**cfg)
+    params = model.params()
+    values = init_params(rng, [p.extents for p in params])
+    for p, v in zip(params, values):
+        ctx.set(p, v)
+    ids = rng.integers(0, cfg.get("num_vocabs", 30522), (batch, seq)).astype(np.uint32)
+    mask = np.ones((batch, seq), np.float32)
+    if pad:
+        for i, p in enumerate(rng.integers(0, seq // 4 + 1, batch)):
+            mask[i, seq - p:] = 0
+    logits = model.pass_(ctx.var(ids), ctx.var(mask)).eval(ctx)
+    rc = R.BertConfig(embed_dim=cfg.get("embed_dim", 768), num_vocabs=cfg.get("num_vocabs", 30522),
+                      max_num_tokens=cfg.get("max_num_tokens", 512), hidden_dim=cfg.get("hidden_dim", 3072),
+                      num_layers=cfg.get("num_layers", 12), num_heads=cfg.get("num_heads", 12),
+                      num_classes=cfg.get("num_classes", 2), **ref_kw)
+    rm = R.Bert(rc)
+    rp = rm.params()
+    assert [tuple(p.extents) for p in rp] == [tuple(p.extents) for p in params]  # same traversal order
+    for p, v in zip(rp, values):
+        p.set(v)
+    ref = rm(RV(ids, R.UINT), RV(mask)).eval().numpy()
+    return logits, ref
+
+
+def test_bert_small_vs_oracle(ctx):
+    cfg = dict(embed_dim=64, num_vocabs=150, max_num_tokens=64, hidden_dim=128, num_layers=2, num_heads=2, num_classes=10)
+    got, ref = run_bert(ctx, cfg, batch=3, seq=20, seed=3001, pad=True)
+    assert got.shape == (3, 10) and rel_err(got, ref, floor=1e-3) <= 1e-3
+
+
+def test_bert_gelu_variant_vs_oracle(ctx):
+    cfg = dict(embed_dim=64, num_vocabs=150, max_num_tokens=64, hidden_dim=128, num_layers=2, num_heads=2, num_classes=4,
+               gelu=1, layer_norm_eps=1e-12)
+    got, ref = run_bert(ctx, cfg, batch=2, seq=16, seed=3002, gelu=True, ln_eps=1e-12)
+    assert rel_err(got, ref, floor=1e-3) <= 1e-3
+
+
+def test_bert_base_vs_oracle(ctx):
+    """BASELINE config 3 at reduced batch (the oracle's sequential-k CPU GEMM sets the time):
+    the reference's BertConfig::base(), seq 128, batch 2."""
+    got, ref = run_bert(ctx, {}, batch=2, seq=128, seed=3001)
+    assert got.shape == (2, 2) and rel_err(got, ref, floor=1e-3) <= 1e-3
+
+
+def test_resnet18_vs_oracle(ctx):
+    rng = np.random.default_rng(5002)
+    model = S.ResNet18(3, 10)
+    params = model.params()
+    values = []
+    for p in params:
+        if len(p.extents) == 4:
+            fan_in = p.extents[0] * p.extents[1] * p.extents[2]
+            values.append((rng.standard_normal(p.extents) * np.sqrt(2.0 / fan_in)).astype(np.float32))
+        elif len(p.extents) == 2:
+            values.append((rng.standard_normal(p.extents) * 0.02).astype(np.float32))
+        else:
+            values.append((rng.standard_normal(p.extents) * 0.01).astype(np.float32))
+    for p, v in zip(params, values):
+        ctx.set(p, v)
+    x = rng.standard_normal((2, 64, 64, 3)).astype(np.float32)
+    got = model.pass_(ctx.var(x)).eval(ctx)
+    rm = R.resnet18(3, 10)
+    rp = rm.params()
+    assert [tuple(p.extents) for p in rp] == [tuple(p.extents) for p in params]
+    for p, v in zip(rp, values):
+        p.set(v)
+    ref = rm(RV(x)).eval().numpy()
+    assert got.shape == (2, 10) and rel_err(got, ref, floor=1e-3) <= 1e-3
+
+
+# ------------------------------------------------------------------------------ runtime behaviour
+def test_program_cache_and_allocator_reuse(ctx):
+    x = ctx.var(np.ones((256, 256), np.float32))
+    y = S.softmax(x * 2.0 + 1.0, [1])
+    before = ctx.programs_compiled()
+    allocs0 = ctx.mem_stats()["num_device_allocs"]
+    outs = []
+    for i in range(5):
+        ctx.set(x, np.full((256, 256), float(i), np.float32))
+        ctx.clear()
+        outs.append(y.eval(ctx))
+    assert ctx.programs_compiled() == before + 1          # compiled once, replayed 4 times
+    assert ctx.mem_stats()["num_device_allocs"] - allocs0 <= 2  # blocks are recycled, not re-allocated
+    assert all(np.allclose(o, 1.0 / 256) for o in outs)
+    assert ctx.status_word() == 0

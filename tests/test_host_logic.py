@@ -1,0 +1,248 @@
+"""CPU-only checks of the host side: the C-ABI library loads and exports every declared symbol,
+graph construction / shape inference / grad / fusion / state selection behave like the reference,
+generated map kernels compile (real NVRTC, no device needed), and the allocator follows its
+policy.  A planning context (device = -1) records launches and computes nothing."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+import sage_b200 as S
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    names = set()
+    for h in ("sage_cuda.h", "sage_graph.h"):
+        text = open(os.path.join(ROOT, "include", h)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b(sage_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
+
+
+def test_library_exports_every_declared_symbol():
+    syms = declared_symbols()
+    assert len(syms) > 80
+    missing = [s for s in syms if not hasattr(S.lib, s)]
+    assert not missing, missing
+
+
+def test_no_device_means_errors_not_fallbacks():
+    if S.device_count() > 0:
+        pytest.skip("a CUDA device is present")
+    with pytest.raises(S.SageError) as e:
+        S.Context(0)
+    assert e.value.code == 5  # SAGE_ERR_NO_DEVICE
+    ctx = S.Context(-1)
+    x = ctx.var(np.ones((4, 4), np.float32))
+    y = x * 2.0
+    ctx.eval(y)  # planning: compiles + records
+    with pytest.raises(S.SageError) as e:
+        ctx.read(y)  # but there is nothing to read
+    assert e.value.code == 5
+
+
+@pytest.fixture()
+def ctx():
+    c = S.Context(-1)
+    yield c
+    c.close()
+
+
+def test_shapes_broadcast_views(ctx):
+    x = ctx.var(np.zeros((2, 3, 4), np.float32))
+    assert x.transpose(0, 2).extents == (4, 3, 2) and x.transpose(0, 2).strides == (1, 4, 12)
+    assert x.view([6, -1]).extents == (6, 4)
+    assert S.expand(ctx.var(np.zeros((3, 1), np.float32)), [2, 3, 5]).strides == (0, 1, 0)
+    assert x.unsqueeze(1).strides == (12, 0, 4, 1)  # a fresh unit axis has stride 0 (src/shape.rs:190-195)
+    assert x.slice(1, 1, 3).offset == 4 and x.slice(1, 1, 3).extents == (2, 2, 4)
+    assert (x + ctx.var(np.zeros((4,), np.float32))).extents == (2, 3, 4)
+    assert x.sum([0, 2], False).extents == (3,) and x.sum([0, 2], True).extents == (1, 3, 1)
+    assert x.sum(None, False).extents == (1,)
+    assert x.argmax(1).dtype == S.U32 and S.gt(x, 0.0).dtype == S.U32 and x.int().dtype == S.I32
+    for bad in (lambda: x.view([5, -1]), lambda: x + ctx.var(np.zeros((5,), np.float32)), lambda: x.squeeze(0),
+                lambda: S.matmul(x, x), lambda: x.transpose(0, 7)):
+        with pytest.raises(S.SageError) as e:
+            bad()
+        assert e.value.code == 1
+
+
+def test_matmul_shapes(ctx):
+    a = ctx.var(np.zeros((2, 5, 7), np.float32))
+    assert S.matmul(a, ctx.var(np.zeros((7, 3), np.float32))).extents == (2, 5, 3)
+    q = ctx.var(np.zeros((2, 4, 6, 8), np.float32))
+    assert S.matmul_batched(q, q.transpose(-1, -2)).extents == (2, 4, 6, 6)
+    assert S.conv_2d(ctx.var(np.zeros((1, 5, 5, 4), np.float32)), ctx.var(np.zeros((3, 3, 4, 8), np.float32)), 1, 1, 1).extents == (1, 5, 5, 8)
+    assert S.max_pool_2d(ctx.var(np.zeros((2, 112, 112, 64), np.float32)), 3, 2, 1, 1).extents == (2, 56, 56, 64)
+
+
+def test_config1_program_matches_reference_fusion(ctx):
+    """src/session.rs + src/ops.rs::fuse: z = x*y + x*3.14 is ONE variadic kernel with x bound twice and
+    the literal folded in; z is materialised (it has several consumers)."""
+    x = ctx.var(np.zeros((1024, 1024), np.float32))
+    y = ctx.var(np.zeros((1024, 1024), np.float32))
+    lab = ctx.var(np.zeros((1024, 1), np.uint32))
+    z = x * y + x * 3.14
+    loss = S.softmax_cross_entropy(z, lab)
+    ctx.trace_begin()
+    ctx.eval(loss)
+    d = ctx.describe().strip().split("\n")
+    assert d[0] == "variadic{((x0 * x1) + (x2 * sg_lit(0x4048f5c3u)))}(data,data,data)"
+    assert "log_sum_exp(state)" in d[-1] and "gather" in d[-1]
+    assert ctx.trace() == ["sage_map", "lse_rows", "sage_map", "gather", "reduce_g1", "sage_map"]
+    # without pattern fusion the reference's own kernel sequence appears (max, exp, sum, log...)
+    c2 = S.Context(-1, pattern_fusion=0)
+    x2 = c2.var(np.zeros((64, 64), np.float32))
+    c2.trace_begin()
+    c2.eval(S.log_sum_exp(x2, [1]))
+    assert [k.split("_g")[0] for k in c2.trace()] == ["reduce", "sage_map", "reduce", "sage_map"]
+    c2.close()
+
+
+def test_grad_graph_and_program_cache(ctx):
+    x = ctx.var(np.zeros((8, 8), np.float32))
+    y = (x.exp() * x).sum([0, 1], False)
+    gx = x.grad(y)
+    assert gx.extents == (8, 8)
+    ctx.eval(gx)
+    n = ctx.programs_compiled()
+    ctx.clear()
+    ctx.eval(gx)
+    assert ctx.programs_compiled() == n  # same targets, same inputs: compiled program is reused
+    with pytest.raises(S.SageError):
+        S.grad(y, [ctx.var(np.zeros((2,), np.float32))])  # unrelated variable
+
+
+def test_map_kernels_compile_for_every_op(ctx):
+    """Every op of the reference's map tables (src/ops/map.rs:224-302) goes through the CUDA emitter and NVRTC."""
+    f = ctx.var(np.zeros((5, 8), np.float32))
+    for name in S._UN:
+        if name in ("not_",):
+            continue
+        ctx.eval(getattr(f, name)())
+    u = S.gt(f, 0.0)
+    ctx.eval(u.not_(), S.and_(u, u), S.or_(u, u), S.cond(u, f, 1.0))
+    for name in S._BIN:
+        if name in ("and_", "or_"):
+            continue
+        ctx.eval(getattr(S, name + "_" if name == "pow" else name)(f, f.transpose(0, 1).organize().view([5, 8])))
+    i = f.int()
+    ctx.eval(i + i, i * i, S.minimum(i, i), i.float())
+    # generic strided, broadcast and vector paths
+    ctx.eval(f.transpose(0, 1) * 2.0, f + ctx.var(np.zeros((8,), np.float32)), f * ctx.var(np.zeros((5, 1), np.float32)))
+
+
+def test_jit_compile_error_is_reported(ctx):
+    m = ctypes.c_void_p()
+    st = S.lib.sage_module_get(ctx.h, b"this is not CUDA", ctypes.byref(m))
+    assert st == 4 and b"error" in S.lib.sage_last_error(ctx.h)
+
+
+def test_allocator_policy():
+    c = S.Context(-1, mem_capacity_bytes=64 << 20)
+    a = c.alloc(100)  # small pool: 2 MiB segment, 512 B block
+    s = c.mem_stats()
+    assert s["mem_total"] == 2 << 20 and s["mem_used"] == 512 and s["num_device_allocs"] == 1
+    b = c.alloc(3 << 20)  # large pool: 20 MiB segment
+    assert c.mem_stats()["mem_total"] == (2 << 20) + (20 << 20)
+    pa, pb = S.lib.sage_buf_ptr(a), S.lib.sage_buf_ptr(b)
+    c.free(b)
+    b2 = c.alloc(3 << 20)
+    assert S.lib.sage_buf_ptr(b2) == pb and c.mem_stats()["num_device_allocs"] == 2  # reused, no new device allocation
+    c3 = c.alloc(5 << 20)  # carved from the same 20 MiB segment (best fit + split)
+    assert c.mem_stats()["num_device_allocs"] == 2
+    with pytest.raises(S.SageError) as e:
+        c.alloc(60 << 20)
+    assert e.value.code == 2
+    need, total = ctypes.c_uint64(), ctypes.c_uint64()
+    S.lib.sage_last_oom(c.h, ctypes.byref(need), ctypes.byref(total))
+    assert total.value == c.mem_stats()["mem_total"] and need.value > 0
+    for buf in (a, b2, c3):
+        c.free(buf)
+    assert c.mem_stats()["mem_used"] == 0
+    S.lib.sage_release_cached(c.h)
+    assert c.mem_stats()["mem_total"] == 0  # merged back into whole segments and returned
+    assert pa is not None
+    c.close()
+
+
+def test_allocator_reference_mode_without_cache():
+    c = S.Context(-1, use_cache=0, mem_capacity_bytes=1000 << 20)  # the reference's shipped configuration
+    bufs = [c.alloc(1 << 20) for _ in range(3)]
+    assert c.mem_stats()["num_device_allocs"] == 3 and c.mem_stats()["mem_total"] == 3 << 20
+    for b in bufs:
+        c.free(b)
+    assert c.mem_stats()["mem_total"] == 0
+    c.close()
+
+
+def test_oom_evicts_and_recomputes():
+    """Program::exec's out-of-memory path (src/session.rs:259-331): with a tight cap the evaluator drops
+    intermediates and finishes instead of failing."""
+    n = 1 << 20  # 4 MiB tensors
+    cap = 44 << 20  # room for two 20 MiB segments (ten 4 MiB blocks) + the 2 MiB small pool
+    c = S.Context(-1, mem_capacity_bytes=cap)
+    x = c.var(np.zeros((n,), np.float32))
+    a = [x * float(i + 2) + 1.0 for i in range(12)]          # twelve 4 MiB states ...
+    s = [v.sum([0], True) for v in a]                        # ... each needed early (its own sum) ...
+    z = s[0]
+    for v in s[1:]:
+        z = z + v
+    t = [(v * z.expand([n])).sum([0], True) for v in a]      # ... and again late, one at a time
+    out = s[0] * 0.0
+    for v, w in zip(t, s):
+        out = out + v + v * 2.0 + w                           # t_i and s_i have two consumers: they are states
+    c.trace_begin()
+    c.eval(out)
+    assert c.mem_stats()["mem_peak"] <= cap
+    # more than 12 + 12 + 12 map/reduce launches means some states were evicted and recomputed
+    assert len([k for k in c.trace() if k == "sage_map"]) > 24
+    c.close()
+
+
+def test_bert_base_plan():
+    """The whole BERT-base graph compiles; the launch list is what the GPU will run."""
+    c = S.Context(-1)
+    model = S.Bert()
+    params = model.params()
+    assert len(params) == 2 + 2 + 12 * (8 + 2 + 4 + 2) + 2
+    assert params[0].extents == (30522, 768) and params[1].extents == (512, 768) and params[-2].extents == (768, 2)
+    for p in params:
+        c.set(p, np.zeros(p.extents, np.float32))
+    ids = c.var(np.zeros((32, 128), np.uint32))
+    mask = c.var(np.ones((32, 128), np.float32))
+    logits = model.pass_(ids, mask)
+    assert logits.extents == (32, 2)
+    c.trace_begin()
+    c.eval(logits)
+    t = c.trace()
+    assert t.count("layernorm_rows") == 25 and t.count("softmax_rows") == 12
+    gemms = [k for k in t if k.startswith("gemm")]
+    assert len(gemms) == 12 * 8 + 1
+    k0, _ = c.launch_count()
+    c.clear()
+    c.eval(logits)
+    assert c.programs_compiled() == 1 and c.launch_count()[0] - k0 == len(t)
+    assert c.mem_stats()["mem_peak"] < 3 << 30
+    c.close()
+
+
+def test_resnet18_plan():
+    c = S.Context(-1)
+    model = S.ResNet18(3, 1000)
+    params = model.params()
+    assert params[0].extents == (7, 7, 3, 64) and params[-2].extents == (512, 1000)
+    for p in params:
+        c.set(p, np.zeros(p.extents, np.float32))
+    x = c.var(np.zeros((2, 224, 224, 3), np.float32))
+    y = model.pass_(x)
+    assert y.extents == (2, 1000)
+    c.trace_begin()
+    c.eval(y)
+    t = c.trace()
+    assert t.count("max_pool2d") == 1 and t.count("avg_pool2d") == 1
+    assert len([k for k in t if k.startswith("gemm")]) == 21
+    c.close()
