@@ -225,6 +225,8 @@ sage_status sage_ipc_open(sage_ctx *ctx, const uint8_t handle[64], void **peer_p
 sage_status sage_ipc_close(sage_ctx *ctx, void *peer_ptr);
 /* Asynchronous copy local buffer → peer pointer (+ byte offset) on the context's stream. */
 sage_status sage_peer_write(sage_ctx *ctx, void *peer_ptr, size_t peer_offset, const sage_buf *src, size_t src_offset, size_t bytes);
+/* Same, from a raw device address of this context's GPU (e.g. the one sage_var_buffer returns). */
+sage_status sage_peer_write_ptr(sage_ctx *ctx, void *peer_ptr, size_t peer_offset, const void *src_dev, size_t bytes);
 
 /* ------------------------------------------------------------------ introspection (planning + tests) */
 /* Number of kernels / memsets this context has launched (or recorded, on a planning context). */
@@ -232,6 +234,16 @@ sage_status sage_launch_count(sage_ctx *ctx, uint64_t *kernels, uint64_t *memset
 /* Start/stop recording kernel names; sage_trace_get copies a '\n'-separated list. */
 sage_status sage_trace_begin(sage_ctx *ctx);
 sage_status sage_trace_get(sage_ctx *ctx, char *out, size_t out_len, size_t *needed);
+/* Device time per kernel name.  Between begin and end a CUDA event is recorded on the context's
+ * stream in front of every launch; end synchronises and copies "name launches total_ms" lines,
+ * largest first.  (The reference only has host wall time around asynchronous enqueues,
+ * src/session.rs:619,667-676.) */
+/* A pair of CUDA events on the context's stream: start records one, stop records the other,
+ * waits for it and returns the device time between them in milliseconds. */
+sage_status sage_timer_start(sage_ctx *ctx);
+sage_status sage_timer_stop(sage_ctx *ctx, float *milliseconds);
+sage_status sage_profile_begin(sage_ctx *ctx);
+sage_status sage_profile_end(sage_ctx *ctx, char *out, size_t out_len, size_t *needed);
 
 #ifdef __cplusplus
 }

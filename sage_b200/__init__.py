@@ -205,6 +205,43 @@ class Context:
         lib.sage_trace_get(self.h, b, ctypes.c_size_t(n.value + 1), None)
         return [l for l in b.value.decode().split("\n") if l]
 
+    def timer_start(self):
+        self._ck(lib.sage_timer_start(self.h))
+
+    def timer_stop(self):
+        """Device milliseconds between timer_start() and now, on the context's stream (waits)."""
+        ms = ctypes.c_float(0)
+        self._ck(lib.sage_timer_stop(self.h, ctypes.byref(ms)))
+        return ms.value
+
+    def pinned(self, shape, dtype):
+        """A numpy array over pinned host memory (for asynchronous uploads / downloads)."""
+        n = int(np.prod(shape)) * np.dtype(dtype).itemsize
+        p = _P()
+        st = lib.sage_host_alloc(ctypes.c_size_t(max(n, 4)), ctypes.byref(p))
+        if st:
+            raise SageError(st, "pinned host allocation failed")
+        buf = (ctypes.c_char * max(n, 4)).from_address(p.value)
+        arr = np.frombuffer(buf, dtype=dtype, count=int(np.prod(shape))).reshape(shape)
+        self._pinned = getattr(self, "_pinned", []) + [(p, buf)]
+        return arr
+
+    def profile_begin(self):
+        lib.sage_profile_begin(self.h)
+
+    def profile_end(self):
+        """Returns {kernel name: (launches, total_ms)} of device time since profile_begin()."""
+        n = ctypes.c_size_t(0)
+        lib.sage_profile_end(self.h, None, ctypes.c_size_t(0), ctypes.byref(n))
+        b = ctypes.create_string_buffer(n.value + 1)
+        lib.sage_profile_end(self.h, b, ctypes.c_size_t(n.value + 1), None)
+        out = {}
+        for line in b.value.decode().split("\n"):
+            parts = line.split()
+            if len(parts) == 3:
+                out[parts[0]] = (int(parts[1]), float(parts[2]))
+        return out
+
     def status_word(self):
         w = ctypes.c_uint32(0)
         self._ck(lib.sage_status_word(self.h, ctypes.byref(w)))

@@ -443,6 +443,12 @@ sage_status sage_ipc_close(sage_ctx *ctx, void *peer_ptr) {
     return C.check_cuda(cudaIpcCloseMemHandle(peer_ptr), "cudaIpcCloseMemHandle");
 }
 
+sage_status sage_peer_write_ptr(sage_ctx *ctx, void *peer_ptr, size_t peer_off, const void *src_dev, size_t bytes) {
+    CTX_OR_FAIL(ctx);
+    if (C.dry()) return C.fail(SAGE_ERR_NO_DEVICE, "peer copy on a planning context");
+    return C.check_cuda(cudaMemcpyAsync((char *)peer_ptr + peer_off, src_dev, bytes, cudaMemcpyDeviceToDevice, C.stream()), "peer copy");
+}
+
 sage_status sage_peer_write(sage_ctx *ctx, void *peer_ptr, size_t peer_off, const sage_buf *src, size_t src_off, size_t bytes) {
     CTX_OR_FAIL(ctx);
     if (C.dry()) return C.fail(SAGE_ERR_NO_DEVICE, "peer copy on a planning context");
@@ -462,6 +468,47 @@ sage_status sage_trace_begin(sage_ctx *ctx) {
     CTX_OR_FAIL(ctx);
     C.tracing = true;
     C.trace.clear();
+    return SAGE_OK;
+}
+
+sage_status sage_timer_start(sage_ctx *ctx) {
+    CTX_OR_FAIL(ctx);
+    if (C.dry()) return C.fail(SAGE_ERR_NO_DEVICE, "timer on a planning context");
+    if (!C.timer_events[0]) {
+        cudaEvent_t a, b;
+        if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return C.fail(SAGE_ERR_DEVICE, "cudaEventCreate");
+        C.timer_events[0] = a;
+        C.timer_events[1] = b;
+    }
+    return C.check_cuda(cudaEventRecord((cudaEvent_t)C.timer_events[0], C.stream()), "event record");
+}
+
+sage_status sage_timer_stop(sage_ctx *ctx, float *ms) {
+    CTX_OR_FAIL(ctx);
+    if (C.dry() || !C.timer_events[0]) return C.fail(SAGE_ERR_INVALID, "timer was not started");
+    sage_status st = C.check_cuda(cudaEventRecord((cudaEvent_t)C.timer_events[1], C.stream()), "event record");
+    if (st) return st;
+    st = C.check_cuda(cudaEventSynchronize((cudaEvent_t)C.timer_events[1]), "event sync");
+    if (st) return st;
+    return C.check_cuda(cudaEventElapsedTime(ms, (cudaEvent_t)C.timer_events[0], (cudaEvent_t)C.timer_events[1]), "event elapsed");
+}
+
+sage_status sage_profile_begin(sage_ctx *ctx) {
+    CTX_OR_FAIL(ctx);
+    C.profile_begin();
+    return SAGE_OK;
+}
+
+sage_status sage_profile_end(sage_ctx *ctx, char *out, size_t out_len, size_t *needed) {
+    CTX_OR_FAIL(ctx);
+    static thread_local std::string last;
+    if (C.profiling) last = C.profile_end();  // a second call with a larger buffer re-reads the same text
+    if (needed) *needed = last.size() + 1;
+    if (out && out_len) {
+        size_t n = last.size() < out_len - 1 ? last.size() : out_len - 1;
+        memcpy(out, last.data(), n);
+        out[n] = 0;
+    }
     return SAGE_OK;
 }
 

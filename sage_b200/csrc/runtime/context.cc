@@ -7,6 +7,7 @@
 #include <nvrtc.h>
 #include <sys/stat.h>
 
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -238,6 +239,50 @@ sage_status Context::launch(Module *m, const char *name, const uint32_t grid[3],
     int e = d.LaunchKernel(fn, grid[0], grid[1], grid[2], block[0], block[1], block[2], smem, stream_, params, nullptr);
     if (e) return fail(SAGE_ERR_DEVICE, std::string("cuLaunchKernel(") + name + "): " + cu_err(e));
     return SAGE_OK;
+}
+
+// ---- per-kernel timing with events in front of every launch
+void Context::profile_begin() {
+    prof_used_ = 0;
+    prof_names_.clear();
+    profiling = !dry();
+}
+
+void Context::profile_mark(const char *name) {
+    if (prof_used_ == prof_events_.size()) {
+        cudaEvent_t ev;
+        if (cudaEventCreate(&ev) != cudaSuccess) {
+            profiling = false;
+            return;
+        }
+        prof_events_.push_back(ev);
+    }
+    cudaEventRecord((cudaEvent_t)prof_events_[prof_used_++], stream_);
+    prof_names_.push_back(name);
+}
+
+std::string Context::profile_end() {
+    std::string out;
+    if (!profiling) return out;
+    profile_mark("");  // closing event
+    profiling = false;
+    cudaStreamSynchronize(stream_);
+    std::map<std::string, std::pair<uint64_t, double>> acc;
+    for (size_t i = 0; i + 1 < prof_used_; ++i) {
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, (cudaEvent_t)prof_events_[i], (cudaEvent_t)prof_events_[i + 1]);
+        auto &a = acc[prof_names_[i]];
+        a.first += 1;
+        a.second += ms;
+    }
+    std::vector<std::pair<std::string, std::pair<uint64_t, double>>> rows(acc.begin(), acc.end());
+    std::sort(rows.begin(), rows.end(), [](const auto &a, const auto &b) { return a.second.second > b.second.second; });
+    char line[256];
+    for (auto &r : rows) {
+        snprintf(line, sizeof line, "%s %llu %.6f\n", r.first.c_str(), (unsigned long long)r.second.first, r.second.second);
+        out += line;
+    }
+    return out;
 }
 
 }  // namespace sage

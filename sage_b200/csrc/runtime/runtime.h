@@ -121,12 +121,23 @@ public:
     void note_launch(const char *name) {
         ++kernel_launches;
         if (tracing) trace.append(name).push_back('\n');
+        if (profiling) profile_mark(name);
     }
     void note_memset() { ++memset_launches; }
     uint64_t kernel_launches = 0, memset_launches = 0;
     bool tracing = false;
     std::string trace;
 
+    // Per-kernel device timing: a CUDA event is recorded on the stream in front of every launch;
+    // on an in-order stream the time between two consecutive events is the time the earlier
+    // launch took (plus any gap before the next one was enqueued).
+    bool profiling = false;
+    void profile_begin();
+    void profile_mark(const char *name);
+    // "name launches total_ms\n" per kernel name, sorted by total time; stops profiling.
+    std::string profile_end();
+
+    void *timer_events[2] = {nullptr, nullptr};  // cudaEvent_t pair of sage_timer_start/stop
     uint32_t *status_word_dev = nullptr;  // device word kernels OR error bits into
     int sm_count = 148;
 
@@ -138,6 +149,9 @@ private:
     std::shared_ptr<Allocator> alloc_;
     std::string last_error_;
     std::unordered_map<std::string, std::unique_ptr<Module>> modules_;
+    std::vector<void *> prof_events_;  // cudaEvent_t pool, reused across profile runs
+    std::vector<std::string> prof_names_;
+    size_t prof_used_ = 0;
 };
 
 }  // namespace sage
