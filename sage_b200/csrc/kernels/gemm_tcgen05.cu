@@ -1,6 +1,428 @@
+// fp32 GEMM on the Blackwell tensor cores: tcgen05.mma (kind::tf32) with TMEM accumulators, operands
+// staged by TMA into 128B-swizzled shared memory, 3xTF32 so results stay at fp32 accuracy.
+//
+// Reference: Gemm::compute_direct / GemmBatched::compute_direct (src/ops/gemm.rs:176-250, 338-421) run
+// CLBlast's scalar "XgemmDirect" OpenCL kernel (src/ops/kernels/matmul_direct.opencl:514-709); the
+// reference has no tensor-core path at all.  Same contract here: row-major C[M,N] = op(A) * op(B),
+// all four transpose modes, strided batches, any M/N/K.
+//
+// 3xTF32.  Each fp32 operand is split once into hi = tf32(a) (round to nearest) and lo = a - hi, and
+//   C = A_hi*B_hi + A_lo*B_hi + A_hi*B_lo
+// is accumulated in fp32 in TMEM; the dropped lo*lo term and the truncation of lo are ~2^-22
+// relative.  The split is a separate pass (split_tf32_kernel) that also re-lays the operand out with a
+// row pitch that is a multiple of 16 bytes, so TMA can read operands whose original leading
+// dimension it could not (e.g. K = 147 of the first ResNet convolution).
+//
+// Kernel structure (one CTA per 128 x BN output tile, 192 threads):
+//   warp 0      one lane issues the TMA loads of a K-block (A_hi, A_lo, B_hi, B_lo) into a ring of stages
+//   warp 1      allocates TMEM; one lane issues 4 k-steps x 3 tcgen05.mma per stage, then commits
+//   warps 2-5   epilogue: tcgen05.ld the 128 x BN accumulator (one TMEM lane = one row) and store C
+// Stages are handed over with mbarriers (full: TMA -> MMA, empty: tcgen05.commit -> TMA).  No
+// cluster launch and no multicast: each CTA loads its own operands.
+//
+// Every wait is bounded: after ~1 s it records SAGE_ERR_TIMEOUT in the context's status word, and
+// the CTA drains (waits, again bounded, for its loads in flight), frees its TMEM and returns.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
 #include "kernels.h"
+
 namespace sage {
+void *driver_symbol(const char *name);  // runtime/context.cc
 namespace k {
-sage_status gemm_tcgen05(Context &, const GemmArgs &) { return SAGE_ERR_UNSUPPORTED; }
+
+namespace {
+constexpr int BM = 128, BK = 32;          // BK * 4 bytes = one 128-byte swizzle row
+constexpr int kThreads = 192;
+constexpr long long kTimeoutCycles = 2000000000LL;  // ~1 s
+
+struct TcParams {
+    float *c;
+    long long ldc, stride_c;
+    int m, n, k;
+    int bn;            // tile width: 64, 128, 192 or 256
+    int stages;
+    int a_kmajor, b_kmajor;
+    unsigned *status;  // device status word
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait: returns false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity) {
+    const unsigned addr = smem_u32(bar);
+    const long long t0 = clock64();
+    for (;;) {
+        unsigned ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (clock64() - t0 > kTimeoutCycles) return false;
+    }
+}
+
+__device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, unsigned long long *bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor for tcgen05.mma: start address, leading / stride byte offsets
+// (all >> 4), descriptor version 1 (bits 46-47), layout type in bits 61-63: 2 = 128-byte swizzle
+// (16-byte chunks, used for K-major tiles), 1 = 128-byte swizzle with a 32-byte base, the only
+// layout the tensor core accepts for MN-major 32-bit (tf32) operands.
+__device__ __forceinline__ unsigned long long smem_desc(unsigned addr, unsigned lbo_bytes, unsigned sbo_bytes, unsigned layout_type) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr >> 4) & 0x3fff);
+    d |= (unsigned long long)((lbo_bytes >> 4) & 0x3fff) << 16;
+    d |= (unsigned long long)((sbo_bytes >> 4) & 0x3fff) << 32;
+    d |= 1ull << 46;
+    d |= (unsigned long long)layout_type << 61;
+    return d;
+}
+
+__device__ __forceinline__ void umma_tf32(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void flag_timeout(const TcParams &p, volatile int *abort_flag, unsigned where) {
+    atomicOr(p.status, 0x100u | where);  // bit 8 = "a tcgen05 GEMM wait timed out", low bits = which wait
+    *abort_flag = 1;
+}
+
+// Loads one operand tile of a K-block into shared memory.  K-major operand (its K axis is contiguous
+// in memory): one box of {32 k, rows}.  MN-major operand: rows/32 boxes of {32 mn, 32 k}, each a
+// 4 KiB block, so that 8 consecutive k rows form one 1024-byte swizzle atom.
+__device__ __forceinline__ void load_operand(const CUtensorMap *map, char *dst, unsigned long long *bar, bool kmajor, int rows,
+                                             int mn0, int k0, int batch, int plane) {
+    if (kmajor) {
+        tma_load_4d(dst, map, bar, k0, mn0, batch, plane);
+    } else {
+        for (int j = 0; j < rows / 32; ++j) tma_load_4d(dst + j * (BK * 128), map, bar, mn0 + 32 * j, k0, batch, plane);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
+    extern __shared__ __align__(1024) char smem_raw[];
+    __shared__ __align__(8) unsigned long long full_bar[8], empty_bar[8], accum_bar;
+    __shared__ unsigned tmem_base_slot;
+    __shared__ volatile int abort_flag;
+
+    // dynamic shared memory is only guaranteed 16-byte aligned; swizzled tiles need 1024
+    char *smem = reinterpret_cast<char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int a_bytes = BM * BK * 4, b_bytes = p.bn * BK * 4;
+    const int stage_bytes = 2 * a_bytes + 2 * b_bytes;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * p.bn, batch = blockIdx.z;
+    const int num_kb = (p.k + BK - 1) / BK;
+    const unsigned tmem_cols = p.bn <= 64 ? 64u : p.bn <= 128 ? 128u : 256u;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&accum_bar, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_d = tmem_base_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        int issued = 0;
+        for (int kb = 0; kb < num_kb && !abort_flag; ++kb) {
+            const int s = kb % p.stages;
+            const unsigned phase = (kb / p.stages) & 1;
+            if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
+                flag_timeout(p, &abort_flag, 1);
+                break;
+            }
+            char *st = smem + (size_t)s * stage_bytes;
+            mbar_expect_tx(&full_bar[s], (unsigned)stage_bytes);
+            load_operand(&map_a, st, &full_bar[s], p.a_kmajor, BM, m0, kb * BK, batch, 0);
+            load_operand(&map_a, st + a_bytes, &full_bar[s], p.a_kmajor, BM, m0, kb * BK, batch, 1);
+            load_operand(&map_b, st + 2 * a_bytes, &full_bar[s], p.b_kmajor, p.bn, n0, kb * BK, batch, 0);
+            load_operand(&map_b, st + 2 * a_bytes + b_bytes, &full_bar[s], p.b_kmajor, p.bn, n0, kb * BK, batch, 1);
+            issued = kb + 1;
+        }
+        // Do not leave the CTA with bulk copies still landing in its shared memory.
+        for (int kb = issued > p.stages ? issued - p.stages : 0; kb < issued; ++kb)
+            if (!mbar_wait(&full_bar[kb % p.stages], (kb / p.stages) & 1)) flag_timeout(p, &abort_flag, 2);
+    } else if (warp == 1 && lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer
+        // instruction descriptor: D = f32, A = B = tf32, majors, N >> 3, M >> 4
+        const unsigned idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((p.a_kmajor ? 0u : 1u) << 15) | ((p.b_kmajor ? 0u : 1u) << 16) |
+                               ((unsigned)(p.bn >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+        // K-major tile: 8-row groups 1024 B apart (stride offset), a k-step is 32 B further along the
+        // swizzled row.  MN-major tile: 32-wide column blocks BK*128 B apart (leading offset), groups of
+        // 4 k-rows 512 B apart (stride offset), a k-step (8 k-rows) is 1024 B further.
+        const unsigned a_lbo = p.a_kmajor ? 16u : (unsigned)(BK * 128), a_step = p.a_kmajor ? 32u : 1024u;
+        const unsigned b_lbo = p.b_kmajor ? 16u : (unsigned)(BK * 128), b_step = p.b_kmajor ? 32u : 1024u;
+        const unsigned a_sbo = p.a_kmajor ? 1024u : 512u, b_sbo = p.b_kmajor ? 1024u : 512u;
+        const unsigned a_lt = p.a_kmajor ? 2u : 1u, b_lt = p.b_kmajor ? 2u : 1u;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb && !abort_flag; ++kb) {
+            const int s = kb % p.stages;
+            const unsigned phase = (kb / p.stages) & 1;
+            if (!mbar_wait(&full_bar[s], phase)) {
+                flag_timeout(p, &abort_flag, 4);
+                ok = false;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const unsigned a_hi = smem_u32(smem + (size_t)s * stage_bytes), a_lo = a_hi + a_bytes;
+            const unsigned b_hi = a_hi + 2 * a_bytes, b_lo = b_hi + b_bytes;
+#pragma unroll
+            for (int ks = 0; ks < BK / 8; ++ks) {
+                const unsigned long long da_hi = smem_desc(a_hi + ks * a_step, a_lbo, a_sbo, a_lt), da_lo = smem_desc(a_lo + ks * a_step, a_lbo, a_sbo, a_lt);
+                const unsigned long long db_hi = smem_desc(b_hi + ks * b_step, b_lbo, b_sbo, b_lt), db_lo = smem_desc(b_lo + ks * b_step, b_lbo, b_sbo, b_lt);
+                umma_tf32(tmem_d, da_lo, db_hi, idesc, (kb | ks) ? 1u : 0u);  // small terms first
+                umma_tf32(tmem_d, da_hi, db_lo, idesc, 1u);
+                umma_tf32(tmem_d, da_hi, db_hi, idesc, 1u);
+            }
+            umma_commit(&empty_bar[s]);  // arrives when the MMAs above have finished reading this stage
+        }
+        if (ok) umma_commit(&accum_bar);
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------------ epilogue
+        const int q = warp & 3;  // TMEM lane quarter this warp may access
+        bool ok = num_kb > 0 ? mbar_wait(&accum_bar, 0) : true;
+        if (!ok && lane == 0) flag_timeout(p, &abort_flag, 8);
+        ok = __all_sync(0xffffffffu, ok && !abort_flag);  // the TMEM loads below are warp-collective
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int row = m0 + q * 32 + lane;
+        float *crow = p.c + (size_t)batch * p.stride_c + (size_t)row * p.ldc;
+        const bool vec_ok = (p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.c) + (size_t)batch * p.stride_c * 4) % 16 == 0);
+        for (int cb = 0; cb < p.bn / 32; ++cb) {
+            unsigned r[32];
+            if (ok && num_kb > 0) {
+                tmem_ld32(tmem_d + ((unsigned)(q * 32) << 16) + (unsigned)(cb * 32), r);  // warp-collective
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = 0u;
+            }
+            const int col0 = n0 + cb * 32;
+            if (!ok || row >= p.m || col0 >= p.n) continue;
+            if (vec_ok && col0 + 32 <= p.n) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4 *>(crow + col0 + j) =
+                        make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.n) crow[col0 + j] = __uint_as_float(r[j]);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------- operand split
+// src: `rows` x `cols` with row stride `ld`, `batches` of them `batch_stride` apart.
+// dst: [2][batches][rows][pitch] with pitch = cols rounded up to 4; plane 0 = tf32(x) rounded to
+// nearest, plane 1 = x - plane 0 (exact in fp32).  Pad columns are written as zeros.
+__global__ void __launch_bounds__(256) split_tf32_kernel(const float *__restrict__ src, long long ld, long long batch_stride, int rows,
+                                                         int cols, int batches, float *__restrict__ dst, int pitch, long long plane_stride) {
+    const int groups = pitch >> 2;
+    const long long total = (long long)batches * rows * groups;
+    const bool vec_in = (ld % 4 == 0) && (batch_stride % 4 == 0) && (reinterpret_cast<uintptr_t>(src) % 16 == 0);
+    for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(g % groups) * 4;
+        const long long rb = g / groups;
+        const int r = (int)(rb % rows);
+        const long long b = rb / rows;
+        const float *s = src + b * batch_stride + (long long)r * ld + c;
+        float x[4];
+        if (vec_in && c + 4 <= cols) {
+            const float4 v = *reinterpret_cast<const float4 *>(s);
+            x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) x[j] = (c + j < cols) ? s[j] : 0.f;
+        }
+        float hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            unsigned h;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x[j]));
+            float hf = __uint_as_float(h);
+            if (!isfinite(hf)) {  // rounding overflowed, or x itself is inf/nan: keep the truncated value, no low part
+                hf = __uint_as_float(__float_as_uint(x[j]) & 0xffffe000u);
+                lo[j] = isfinite(x[j]) ? x[j] - hf : 0.f;
+            } else {
+                lo[j] = x[j] - hf;
+            }
+            hi[j] = hf;
+        }
+        float *d = dst + (b * rows + r) * (long long)pitch + c;
+        *reinterpret_cast<float4 *>(d) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<float4 *>(d + plane_stride) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+    }
+}
+
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                    const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct SplitOperand {
+    Block *block = nullptr;
+    float *planes = nullptr;
+    int rows = 0, cols = 0, pitch = 0, batches = 0;
+};
+
+// Splits one operand as it lies in memory (`rows` x `cols`, cols contiguous).
+static sage_status split_operand(Context &ctx, const float *src, long long ld, long long batch_stride, int rows, int cols, int batches,
+                                 SplitOperand *out) {
+    out->rows = rows;
+    out->cols = cols;
+    out->batches = batches;
+    out->pitch = (cols + 3) / 4 * 4;
+    const size_t plane = (size_t)batches * rows * out->pitch;
+    out->block = ctx.allocator().alloc(plane * 2 * sizeof(float));
+    if (!out->block) return ctx.fail(SAGE_ERR_OOM, "out of memory for the tf32 operand split");
+    out->planes = reinterpret_cast<float *>(out->block->ptr);
+    ctx.note_launch("split_tf32");
+    if (ctx.dry()) return SAGE_OK;
+    const long long total = (long long)plane / 4;
+    long long blocks = (total + 255) / 256;
+    const long long cap = (long long)ctx.sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    split_tf32_kernel<<<(unsigned)blocks, 256, 0, ctx.stream()>>>(src, ld, batch_stride, rows, cols, batches, out->planes, out->pitch,
+                                                                  (long long)plane);
+    return ctx.check_cuda(cudaGetLastError(), "split_tf32 launch");
+}
+
+// 4-D tensor map {cols, rows, batch, plane} over a split operand with a {32, box_rows, 1, 1} box.
+static bool encode_map(PFN_encodeTiled encode, const SplitOperand &op, unsigned box_rows, bool kmajor, CUtensorMap *map) {
+    const cuuint64_t dims[4] = {(cuuint64_t)op.cols, (cuuint64_t)op.rows, (cuuint64_t)op.batches, 2};
+    const cuuint64_t row_b = (cuuint64_t)op.pitch * 4;
+    const cuuint64_t strides[3] = {row_b, row_b * op.rows, row_b * op.rows * op.batches};
+    const cuuint32_t box[4] = {32, box_rows, 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, op.planes, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  kmajor ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int pick_bn(const Context &ctx, long long m, long long n, long long batch) {
+    const int cands[4] = {256, 192, 128, 64};
+    int best = 128;
+    double best_cost = 1e300;
+    for (int bn : cands) {
+        if (bn > 64 && n <= bn / 2) continue;  // mostly padding
+        const long long tiles = ((n + bn - 1) / bn) * ((m + BM - 1) / BM) * batch;
+        const long long waves = (tiles + ctx.sm_count - 1) / ctx.sm_count;
+        const double cost = (double)waves * (bn + 24);  // +24: per-tile fixed cost in units of columns
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    return best;
+}
+}  // namespace
+
+sage_status gemm_tcgen05(Context &ctx, const GemmArgs &g) {
+    // Tiny problems are latency-bound and would be mostly TMA padding: leave them to the SIMT kernel.
+    if (g.m < 64 || g.n < 32 || g.k < 32 || g.batch < 1) return SAGE_ERR_UNSUPPORTED;
+    if (g.m > 0x7fffffffLL || g.n > 0x7fffffffLL || g.k > 0x7fffffffLL || g.batch > 65535) return SAGE_ERR_UNSUPPORTED;
+    if ((g.m + BM - 1) / BM > 65535) return SAGE_ERR_UNSUPPORTED;
+    static PFN_encodeTiled encode = nullptr;
+    if (!ctx.dry() && !encode) {
+        encode = reinterpret_cast<PFN_encodeTiled>(driver_symbol("cuTensorMapEncodeTiled"));
+        if (!encode) return SAGE_ERR_UNSUPPORTED;
+    }
+    const int bn = pick_bn(ctx, g.m, g.n, g.batch);
+    const int stage_bytes = 2 * BM * BK * 4 + 2 * bn * BK * 4;
+    int stages = (227 * 1024 - 2048) / stage_bytes;
+    if (stages > 4) stages = 4;
+    const size_t smem = (size_t)stages * stage_bytes + 1024;
+
+    // A as stored: [M,K] (K-major) or, transposed, [K,M] (MN-major); B: [K,N] (MN-major) or [N,K] (K-major).
+    SplitOperand a, b;
+    sage_status st = split_operand(ctx, g.a, g.lda, g.stride_a, g.ta ? (int)g.k : (int)g.m, g.ta ? (int)g.m : (int)g.k, (int)g.batch, &a);
+    if (st) return st;
+    st = split_operand(ctx, g.b, g.ldb, g.stride_b, g.tb ? (int)g.n : (int)g.k, g.tb ? (int)g.k : (int)g.n, (int)g.batch, &b);
+    if (st) {
+        ctx.allocator().free(a.block);
+        return st;
+    }
+    const bool a_kmajor = !g.ta, b_kmajor = g.tb;
+    ctx.note_launch("gemm_tc_3xtf32");
+    if (!ctx.dry()) {
+        CUtensorMap map_a, map_b;
+        if (!encode_map(encode, a, a_kmajor ? BM : 32, a_kmajor, &map_a) || !encode_map(encode, b, b_kmajor ? (unsigned)bn : 32, b_kmajor, &map_b)) {
+            ctx.allocator().free(a.block);
+            ctx.allocator().free(b.block);
+            return ctx.fail(SAGE_ERR_DEVICE, "cuTensorMapEncodeTiled failed");
+        }
+        // per device; the limit covers dynamic + static shared memory, so ask for what is used
+        st = ctx.check_cuda(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                            "gemm_tc shared memory attribute");
+        if (st) {
+            ctx.allocator().free(a.block);
+            ctx.allocator().free(b.block);
+            return st;
+        }
+        TcParams p{g.c, g.ldc, g.stride_c, (int)g.m, (int)g.n, (int)g.k, bn, stages, a_kmajor ? 1 : 0, b_kmajor ? 1 : 0, ctx.status_word_dev};
+        dim3 grid((unsigned)((g.n + bn - 1) / bn), (unsigned)((g.m + BM - 1) / BM), (unsigned)g.batch);
+        gemm_tc_kernel<<<grid, kThreads, smem, ctx.stream()>>>(map_a, map_b, p);
+        st = ctx.check_cuda(cudaGetLastError(), "gemm_tc launch");
+    }
+    // Stream-ordered: the split buffers may be reused by later launches on this stream.
+    ctx.allocator().free(a.block);
+    ctx.allocator().free(b.block);
+    return st;
+}
+
 }  // namespace k
 }  // namespace sage
