@@ -62,7 +62,19 @@ struct TensorDesc {
 
 // ---------------------------------------------------------------- Tensor (src/tensor.rs:106-110)
 // Device memory returns to the allocator when the last handle drops (OpenClMemory, memory.rs:672-692).
+// The tf32 hi/lo split of (a view of) a storage, kept next to it so that weights and activations
+// read by several GEMMs are split once.  Dropped with the storage, or when the storage is rewritten.
+struct SplitCache {
+    k::SplitPlanes planes;
+    std::shared_ptr<Allocator> alloc;
+    long long offset = 0, ld = 0, batch_stride = 0;  // the view that was split
+    ~SplitCache() {
+        if (alloc && planes.block) alloc->free(planes.block);
+    }
+};
+
 struct Storage {
+    std::shared_ptr<SplitCache> split;
     Context *ctx = nullptr;  // identity only; never dereferenced by the destructor
     std::shared_ptr<Allocator> alloc;
     Block *block = nullptr;

@@ -43,7 +43,35 @@ struct GemmOp : Operator {
         g.stride_a = batched ? a.strides[0] : 0;
         g.stride_b = batched ? b.strides[0] : 0;
         g.stride_c = g.m * g.n;
-        return k::gemm(ctx, g);
+        if (ctx.opts().gemm_backend == 1 || !k::gemm_tc_supported(g)) return k::gemm_simt(ctx, g);
+        // Tensor-core path: each operand's hi/lo split is cached on its storage.
+        std::shared_ptr<SplitCache> sa, sb;
+        st = split_of(ctx, x[0], g.lda, g.stride_a, ta ? g.k : g.m, ta ? g.m : g.k, g.batch, &sa);
+        if (st) return st;
+        st = split_of(ctx, x[1], g.ldb, g.stride_b, tb ? g.n : g.k, tb ? g.k : g.n, g.batch, &sb);
+        if (st) return st;
+        return k::gemm_tcgen05_planes(ctx, g, sa->planes, sb->planes);
+    }
+
+    static sage_status split_of(Context &ctx, const Tensor &t, long long ld, long long batch_stride, long long rows, long long cols,
+                                long long batches, std::shared_ptr<SplitCache> *out) {
+        std::shared_ptr<SplitCache> &c = t.data->split;
+        const long long off = t.desc.shape.offset;
+        if (c && c->offset == off && c->ld == ld && c->batch_stride == batch_stride && c->planes.rows == rows && c->planes.cols == cols &&
+            c->planes.batches == batches) {
+            *out = c;
+            return SAGE_OK;
+        }
+        auto fresh = std::make_shared<SplitCache>();
+        fresh->alloc = ctx.allocator_ptr();
+        fresh->offset = off;
+        fresh->ld = ld;
+        fresh->batch_stride = batch_stride;
+        sage_status st = k::split_tf32(ctx, (const float *)t.ptr(), ld, batch_stride, (int)rows, (int)cols, (int)batches, &fresh->planes);
+        if (st) return st;
+        c = fresh;
+        *out = fresh;
+        return SAGE_OK;
     }
 };
 

@@ -7,21 +7,28 @@
 // all four transpose modes, strided batches, any M/N/K.
 //
 // 3xTF32.  Each fp32 operand is split once into hi = tf32(a) (round to nearest) and lo = a - hi, and
-//   C = A_hi*B_hi + A_lo*B_hi + A_hi*B_lo
-// is accumulated in fp32 in TMEM; the dropped lo*lo term and the truncation of lo are ~2^-22
-// relative.  The split is a separate pass (split_tf32_kernel) that also re-lays the operand out with a
-// row pitch that is a multiple of 16 bytes, so TMA can read operands whose original leading
-// dimension it could not (e.g. K = 147 of the first ResNet convolution).
+//   C = A_lo*B_hi + A_hi*B_lo + A_hi*B_hi
+// The split is a separate pass (split_tf32_kernel) that also re-lays the operand out with a row pitch
+// that is a multiple of 16 bytes, so TMA can read operands whose original leading dimension it could
+// not (e.g. K = 147 of the first ResNet convolution).  Callers may keep the split of an operand
+// (weights, activations read by several GEMMs) and pass it again.
 //
-// Kernel structure (one CTA per 128 x BN output tile, 192 threads):
+// Accumulation.  The tensor core adds into its fp32 accumulator with truncation, which biases a
+// long chain: measured on B200, 3072 chained MMAs (K = 8192) were ~17x less accurate than a plain
+// fp32 loop.  So a chain is cut every kChunkKB K-blocks (128 k): each chunk accumulates in TMEM from
+// zero, and the epilogue warps add the finished chunk into fp32 registers with round-to-nearest
+// while the tensor core already works on the next chunk in the other TMEM buffer.
+//
+// Kernel structure (persistent: one CTA per SM walks over 128 x BN output tiles; 320 threads):
 //   warp 0      one lane issues the TMA loads of a K-block (A_hi, A_lo, B_hi, B_lo) into a ring of stages
-//   warp 1      allocates TMEM; one lane issues 4 k-steps x 3 tcgen05.mma per stage, then commits
-//   warps 2-5   epilogue: tcgen05.ld the 128 x BN accumulator (one TMEM lane = one row) and store C
-// Stages are handed over with mbarriers (full: TMA -> MMA, empty: tcgen05.commit -> TMA).  No
-// cluster launch and no multicast: each CTA loads its own operands.
+//   warp 1      allocates TMEM; one lane issues 4 k-steps x 3 tcgen05.mma per K-block, commits stages/chunks
+//   warps 2-9   epilogue: tcgen05.ld each finished chunk (a TMEM lane = an output row; two warps share a
+//               lane quarter and take half of the columns each), add it to registers, store C at tile end
+// Hand-over by mbarriers: full/empty per shared-memory stage, tmem_full/tmem_empty per TMEM buffer.
+// No cluster launch and no multicast: each CTA loads its own operands.
 //
-// Every wait is bounded: after ~1 s it records SAGE_ERR_TIMEOUT in the context's status word, and
-// the CTA drains (waits, again bounded, for its loads in flight), frees its TMEM and returns.
+// Every wait is bounded: after ~1 s it records a timeout in the context's status word, and the CTA
+// drains (waits, again bounded, for its loads in flight), frees its TMEM and returns.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -32,17 +39,19 @@ void *driver_symbol(const char *name);  // runtime/context.cc
 namespace k {
 
 namespace {
-constexpr int BM = 128, BK = 32;          // BK * 4 bytes = one 128-byte swizzle row
-constexpr int kThreads = 192;
+constexpr int BM = 128, BK = 32;  // BK * 4 bytes = one 128-byte swizzle row
+constexpr int kThreads = 320;
+constexpr int kEpiWarps = 8;
+constexpr int kChunkKB = 4;       // K-blocks per accumulation chain
 constexpr long long kTimeoutCycles = 2000000000LL;  // ~1 s
 
 struct TcParams {
     float *c;
     long long ldc, stride_c;
     int m, n, k;
-    int bn;            // tile width: 64, 128, 192 or 256
     int stages;
     int a_kmajor, b_kmajor;
+    int tiles_m, tiles_n, num_tiles;
     unsigned *status;  // device status word
 };
 
@@ -53,6 +62,9 @@ __device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned coun
 }
 __device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // Bounded wait: returns false when the limit ran out.
 __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity) {
@@ -119,6 +131,17 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ void flag_timeout(const TcParams &p, volatile int *abort_flag, unsigned where) {
     atomicOr(p.status, 0x100u | where);  // bit 8 = "a tcgen05 GEMM wait timed out", low bits = which wait
     *abort_flag = 1;
@@ -126,7 +149,7 @@ __device__ __forceinline__ void flag_timeout(const TcParams &p, volatile int *ab
 
 // Loads one operand tile of a K-block into shared memory.  K-major operand (its K axis is contiguous
 // in memory): one box of {32 k, rows}.  MN-major operand: rows/32 boxes of {32 mn, 32 k}, each a
-// 4 KiB block, so that 8 consecutive k rows form one 1024-byte swizzle atom.
+// 4 KiB block of 32 k-rows x 128 bytes.
 __device__ __forceinline__ void load_operand(const CUtensorMap *map, char *dst, unsigned long long *bar, bool kmajor, int rows,
                                              int mn0, int k0, int batch, int plane) {
     if (kmajor) {
@@ -136,66 +159,83 @@ __device__ __forceinline__ void load_operand(const CUtensorMap *map, char *dst, 
     }
 }
 
+__device__ __forceinline__ void tile_coords(const TcParams &p, int tile, int bn, int *m0, int *n0, int *batch) {
+    const int per_batch = p.tiles_m * p.tiles_n;
+    *batch = tile / per_batch;
+    const int r = tile - *batch * per_batch;
+    *m0 = (r / p.tiles_n) * BM;  // consecutive CTAs share the A rows and take neighbouring B columns
+    *n0 = (r % p.tiles_n) * bn;
+}
+
+template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
     extern __shared__ __align__(1024) char smem_raw[];
-    __shared__ __align__(8) unsigned long long full_bar[8], empty_bar[8], accum_bar;
+    __shared__ __align__(8) unsigned long long full_bar[8], empty_bar[8], tmem_full[2], tmem_empty[2];
     __shared__ unsigned tmem_base_slot;
     __shared__ volatile int abort_flag;
 
+    constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4, STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+    constexpr unsigned BUF_COLS = BN == 192 ? 256u : (unsigned)BN;  // column stride between the two TMEM buffers
+    constexpr unsigned TMEM_COLS = 2 * BUF_COLS;                    // 128, 256 or 512: a power of two
+    constexpr int HALF = BN / 2;                                    // columns per epilogue warp
+
     // dynamic shared memory is only guaranteed 16-byte aligned; swizzled tiles need 1024
     char *smem = reinterpret_cast<char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const int a_bytes = BM * BK * 4, b_bytes = p.bn * BK * 4;
-    const int stage_bytes = 2 * a_bytes + 2 * b_bytes;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * p.bn, batch = blockIdx.z;
     const int num_kb = (p.k + BK - 1) / BK;
-    const unsigned tmem_cols = p.bn <= 64 ? 64u : p.bn <= 128 ? 128u : 256u;
+    const int chunks_per_tile = (num_kb + kChunkKB - 1) / kChunkKB;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
-        mbar_init(&accum_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], kEpiWarps);
+        }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const unsigned tmem_d = tmem_base_slot;
+    const unsigned tmem_base = tmem_base_slot;
 
     if (warp == 0 && lane == 0) {
         // ------------------------------------------------------------------ TMA producer
-        int issued = 0;
-        for (int kb = 0; kb < num_kb && !abort_flag; ++kb) {
-            const int s = kb % p.stages;
-            const unsigned phase = (kb / p.stages) & 1;
-            if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
-                flag_timeout(p, &abort_flag, 1);
-                break;
+        int kbg = 0;  // K-blocks issued so far, across tiles
+        for (int tile = blockIdx.x; tile < p.num_tiles && !abort_flag; tile += gridDim.x) {
+            int m0, n0, batch;
+            tile_coords(p, tile, BN, &m0, &n0, &batch);
+            for (int kb = 0; kb < num_kb; ++kb, ++kbg) {
+                const int s = kbg % p.stages;
+                if (!mbar_wait(&empty_bar[s], ((kbg / p.stages) & 1) ^ 1)) {
+                    flag_timeout(p, &abort_flag, 1);
+                    break;
+                }
+                if (abort_flag) break;
+                char *st = smem + (size_t)s * STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], (unsigned)STAGE_BYTES);
+                load_operand(&map_a, st, &full_bar[s], p.a_kmajor, BM, m0, kb * BK, batch, 0);
+                load_operand(&map_a, st + A_BYTES, &full_bar[s], p.a_kmajor, BM, m0, kb * BK, batch, 1);
+                load_operand(&map_b, st + 2 * A_BYTES, &full_bar[s], p.b_kmajor, BN, n0, kb * BK, batch, 0);
+                load_operand(&map_b, st + 2 * A_BYTES + B_BYTES, &full_bar[s], p.b_kmajor, BN, n0, kb * BK, batch, 1);
             }
-            char *st = smem + (size_t)s * stage_bytes;
-            mbar_expect_tx(&full_bar[s], (unsigned)stage_bytes);
-            load_operand(&map_a, st, &full_bar[s], p.a_kmajor, BM, m0, kb * BK, batch, 0);
-            load_operand(&map_a, st + a_bytes, &full_bar[s], p.a_kmajor, BM, m0, kb * BK, batch, 1);
-            load_operand(&map_b, st + 2 * a_bytes, &full_bar[s], p.b_kmajor, p.bn, n0, kb * BK, batch, 0);
-            load_operand(&map_b, st + 2 * a_bytes + b_bytes, &full_bar[s], p.b_kmajor, p.bn, n0, kb * BK, batch, 1);
-            issued = kb + 1;
         }
         // Do not leave the CTA with bulk copies still landing in its shared memory.
-        for (int kb = issued > p.stages ? issued - p.stages : 0; kb < issued; ++kb)
-            if (!mbar_wait(&full_bar[kb % p.stages], (kb / p.stages) & 1)) flag_timeout(p, &abort_flag, 2);
+        for (int i = kbg > p.stages ? kbg - p.stages : 0; i < kbg; ++i)
+            if (!mbar_wait(&full_bar[i % p.stages], (i / p.stages) & 1)) flag_timeout(p, &abort_flag, 2);
     } else if (warp == 1 && lane == 0) {
         // ------------------------------------------------------------------ MMA issuer
         // instruction descriptor: D = f32, A = B = tf32, majors, N >> 3, M >> 4
         const unsigned idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((p.a_kmajor ? 0u : 1u) << 15) | ((p.b_kmajor ? 0u : 1u) << 16) |
-                               ((unsigned)(p.bn >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+                               ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
         // K-major tile: 8-row groups 1024 B apart (stride offset), a k-step is 32 B further along the
         // swizzled row.  MN-major tile: 32-wide column blocks BK*128 B apart (leading offset), groups of
         // 4 k-rows 512 B apart (stride offset), a k-step (8 k-rows) is 1024 B further.
@@ -203,58 +243,87 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const unsigned b_lbo = p.b_kmajor ? 16u : (unsigned)(BK * 128), b_step = p.b_kmajor ? 32u : 1024u;
         const unsigned a_sbo = p.a_kmajor ? 1024u : 512u, b_sbo = p.b_kmajor ? 1024u : 512u;
         const unsigned a_lt = p.a_kmajor ? 2u : 1u, b_lt = p.b_kmajor ? 2u : 1u;
+        int kbg = 0, cg = 0;  // K-blocks / chunks consumed so far, across tiles
         bool ok = true;
-        for (int kb = 0; kb < num_kb && !abort_flag; ++kb) {
-            const int s = kb % p.stages;
-            const unsigned phase = (kb / p.stages) & 1;
-            if (!mbar_wait(&full_bar[s], phase)) {
-                flag_timeout(p, &abort_flag, 4);
-                ok = false;
-                break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const unsigned a_hi = smem_u32(smem + (size_t)s * stage_bytes), a_lo = a_hi + a_bytes;
-            const unsigned b_hi = a_hi + 2 * a_bytes, b_lo = b_hi + b_bytes;
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+            for (int c = 0; c < chunks_per_tile && ok; ++c, ++cg) {
+                const int buf = cg & 1;
+                if (!mbar_wait(&tmem_empty[buf], ((cg >> 1) & 1) ^ 1)) {  // epilogue has drained this buffer
+                    flag_timeout(p, &abort_flag, 16);
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned tmem_d = tmem_base + (unsigned)buf * BUF_COLS;
+                const int kb_end = min(num_kb, (c + 1) * kChunkKB);
+                for (int kb = c * kChunkKB; kb < kb_end; ++kb, ++kbg) {
+                    const int s = kbg % p.stages;
+                    if (abort_flag || !mbar_wait(&full_bar[s], (kbg / p.stages) & 1)) {
+                        if (!abort_flag) flag_timeout(p, &abort_flag, 4);
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const unsigned a_hi = smem_u32(smem + (size_t)s * STAGE_BYTES), a_lo = a_hi + A_BYTES;
+                    const unsigned b_hi = a_hi + 2 * A_BYTES, b_lo = b_hi + B_BYTES;
 #pragma unroll
-            for (int ks = 0; ks < BK / 8; ++ks) {
-                const unsigned long long da_hi = smem_desc(a_hi + ks * a_step, a_lbo, a_sbo, a_lt), da_lo = smem_desc(a_lo + ks * a_step, a_lbo, a_sbo, a_lt);
-                const unsigned long long db_hi = smem_desc(b_hi + ks * b_step, b_lbo, b_sbo, b_lt), db_lo = smem_desc(b_lo + ks * b_step, b_lbo, b_sbo, b_lt);
-                umma_tf32(tmem_d, da_lo, db_hi, idesc, (kb | ks) ? 1u : 0u);  // small terms first
-                umma_tf32(tmem_d, da_hi, db_lo, idesc, 1u);
-                umma_tf32(tmem_d, da_hi, db_hi, idesc, 1u);
+                    for (int ks = 0; ks < BK / 8; ++ks) {
+                        const unsigned long long da_hi = smem_desc(a_hi + ks * a_step, a_lbo, a_sbo, a_lt), da_lo = smem_desc(a_lo + ks * a_step, a_lbo, a_sbo, a_lt);
+                        const unsigned long long db_hi = smem_desc(b_hi + ks * b_step, b_lbo, b_sbo, b_lt), db_lo = smem_desc(b_lo + ks * b_step, b_lbo, b_sbo, b_lt);
+                        umma_tf32(tmem_d, da_lo, db_hi, idesc, (kb > c * kChunkKB || ks > 0) ? 1u : 0u);  // small terms first
+                        umma_tf32(tmem_d, da_hi, db_lo, idesc, 1u);
+                        umma_tf32(tmem_d, da_hi, db_hi, idesc, 1u);
+                    }
+                    umma_commit(&empty_bar[s]);  // arrives when the MMAs above have finished reading this stage
+                }
+                if (ok) umma_commit(&tmem_full[buf]);
             }
-            umma_commit(&empty_bar[s]);  // arrives when the MMAs above have finished reading this stage
         }
-        if (ok) umma_commit(&accum_bar);
     } else if (warp >= 2) {
-        // ------------------------------------------------------------------ epilogue
-        const int q = warp & 3;  // TMEM lane quarter this warp may access
-        bool ok = num_kb > 0 ? mbar_wait(&accum_bar, 0) : true;
-        if (!ok && lane == 0) flag_timeout(p, &abort_flag, 8);
-        ok = __all_sync(0xffffffffu, ok && !abort_flag);  // the TMEM loads below are warp-collective
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int row = m0 + q * 32 + lane;
-        float *crow = p.c + (size_t)batch * p.stride_c + (size_t)row * p.ldc;
-        const bool vec_ok = (p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.c) + (size_t)batch * p.stride_c * 4) % 16 == 0);
-        for (int cb = 0; cb < p.bn / 32; ++cb) {
-            unsigned r[32];
-            if (ok && num_kb > 0) {
-                tmem_ld32(tmem_d + ((unsigned)(q * 32) << 16) + (unsigned)(cb * 32), r);  // warp-collective
-            } else {
+        // ------------------------------------------------------------------ epilogue (8 warps)
+        const int q = warp & 3;           // TMEM lane quarter this warp may access
+        const int h = (warp - 2) >> 2;    // which half of the tile's columns
+        float acc[HALF];
+        int cg = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+            int m0, n0, batch;
+            tile_coords(p, tile, BN, &m0, &n0, &batch);
+            for (int c = 0; c < chunks_per_tile && ok; ++c, ++cg) {
+                const int buf = cg & 1;
+                bool got = mbar_wait(&tmem_full[buf], (cg >> 1) & 1);
+                if (!got && lane == 0) flag_timeout(p, &abort_flag, 8);
+                ok = __all_sync(0xffffffffu, got && !abort_flag);  // the TMEM loads below are warp-collective
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned taddr = tmem_base + (unsigned)buf * BUF_COLS + ((unsigned)(q * 32) << 16) + (unsigned)(h * HALF);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) r[j] = 0u;
+                for (int j = 0; j < HALF / 16; ++j) {
+                    unsigned r[16];
+                    tmem_ld16(taddr + j * 16, r);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) acc[j * 16 + i] = (c == 0) ? __uint_as_float(r[i]) : acc[j * 16 + i] + __uint_as_float(r[i]);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tmem_empty[buf]);  // this warp no longer needs the buffer
             }
-            const int col0 = n0 + cb * 32;
-            if (!ok || row >= p.m || col0 >= p.n) continue;
-            if (vec_ok && col0 + 32 <= p.n) {
+            if (!ok) break;
+            const int row = m0 + q * 32 + lane;
+            const int col0 = n0 + h * HALF;
+            if (row < p.m && col0 < p.n) {
+                float *crow = p.c + (size_t)batch * p.stride_c + (size_t)row * p.ldc;
+                const bool vec_ok = (p.ldc % 4 == 0) && (p.stride_c % 4 == 0) && (reinterpret_cast<uintptr_t>(p.c) % 16 == 0) &&
+                                    (col0 + HALF <= p.n);
+                if (vec_ok) {
 #pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                    *reinterpret_cast<float4 *>(crow + col0 + j) =
-                        make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-            } else {
+                    for (int j = 0; j < HALF; j += 4)
+                        *reinterpret_cast<float4 *>(crow + col0 + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                } else {
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (col0 + j < p.n) crow[col0 + j] = __uint_as_float(r[j]);
+                    for (int j = 0; j < HALF; ++j)
+                        if (col0 + j < p.n) crow[col0 + j] = acc[j];
+                }
             }
         }
     }
@@ -263,7 +332,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 1) {
         __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -293,9 +362,9 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float *__restrict
         float hi[4], lo[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            unsigned h;
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x[j]));
-            float hf = __uint_as_float(h);
+            unsigned hbits;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hbits) : "f"(x[j]));
+            float hf = __uint_as_float(hbits);
             if (!isfinite(hf)) {  // rounding overflowed, or x itself is inf/nan: keep the truncated value, no low part
                 hf = __uint_as_float(__float_as_uint(x[j]) & 0xffffe000u);
                 lo[j] = isfinite(x[j]) ? x[j] - hf : 0.f;
@@ -314,15 +383,56 @@ typedef CUresult (*PFN_encodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32
                                     const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-struct SplitOperand {
-    Block *block = nullptr;
-    float *planes = nullptr;
-    int rows = 0, cols = 0, pitch = 0, batches = 0;
-};
+// 4-D tensor map {cols, rows, batch, plane} over a split operand with a {32, box_rows, 1, 1} box.
+bool encode_map(PFN_encodeTiled encode, const SplitPlanes &op, unsigned box_rows, bool kmajor, CUtensorMap *map) {
+    const cuuint64_t dims[4] = {(cuuint64_t)op.cols, (cuuint64_t)op.rows, (cuuint64_t)op.batches, 2};
+    const cuuint64_t row_b = (cuuint64_t)op.pitch * 4;
+    const cuuint64_t strides[3] = {row_b, row_b * op.rows, row_b * op.rows * op.batches};
+    const cuuint32_t box[4] = {32, box_rows, 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, op.planes, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  kmajor ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
-// Splits one operand as it lies in memory (`rows` x `cols`, cols contiguous).
-static sage_status split_operand(Context &ctx, const float *src, long long ld, long long batch_stride, int rows, int cols, int batches,
-                                 SplitOperand *out) {
+int pick_bn(const Context &ctx, long long m, long long n, long long batch) {
+    const int cands[4] = {256, 192, 128, 64};
+    int best = 128;
+    double best_cost = 1e300;
+    for (int bn : cands) {
+        if (bn > 64 && n <= bn / 2) continue;  // mostly padding
+        const long long tiles = ((n + bn - 1) / bn) * ((m + BM - 1) / BM) * batch;
+        const long long waves = (tiles + ctx.sm_count - 1) / ctx.sm_count;
+        const double cost = (double)waves * (bn + 24);  // +24: per-tile fixed cost in units of columns
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    return best;
+}
+
+template <int BN>
+sage_status launch_tc(Context &ctx, const CUtensorMap &map_a, const CUtensorMap &map_b, TcParams p, int grid, size_t smem) {
+    // per device; the limit covers dynamic + static shared memory, so ask for what is used
+    sage_status st = ctx.check_cuda(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                                    "gemm_tc shared memory attribute");
+    if (st) return st;
+    gemm_tc_kernel<BN><<<grid, kThreads, smem, ctx.stream()>>>(map_a, map_b, p);
+    return ctx.check_cuda(cudaGetLastError(), "gemm_tc launch");
+}
+}  // namespace
+
+bool gemm_tc_supported(const GemmArgs &g) {
+    // Tiny problems are latency-bound and would be mostly TMA padding: leave them to the SIMT kernel.
+    if (g.m < 64 || g.n < 32 || g.k < 32 || g.batch < 1) return false;
+    if (g.m > 0x7fffffffLL || g.n > 0x7fffffffLL || g.k > 0x7fffffffLL || g.batch > 0x7fffffffLL) return false;
+    const long long tiles = ((g.m + BM - 1) / BM) * ((g.n + 63) / 64) * g.batch;
+    return tiles < 0x7fffffffLL;
+}
+
+sage_status split_tf32(Context &ctx, const float *src, long long ld, long long batch_stride, int rows, int cols, int batches,
+                       SplitPlanes *out) {
     out->rows = rows;
     out->cols = cols;
     out->batches = batches;
@@ -342,85 +452,62 @@ static sage_status split_operand(Context &ctx, const float *src, long long ld, l
     return ctx.check_cuda(cudaGetLastError(), "split_tf32 launch");
 }
 
-// 4-D tensor map {cols, rows, batch, plane} over a split operand with a {32, box_rows, 1, 1} box.
-static bool encode_map(PFN_encodeTiled encode, const SplitOperand &op, unsigned box_rows, bool kmajor, CUtensorMap *map) {
-    const cuuint64_t dims[4] = {(cuuint64_t)op.cols, (cuuint64_t)op.rows, (cuuint64_t)op.batches, 2};
-    const cuuint64_t row_b = (cuuint64_t)op.pitch * 4;
-    const cuuint64_t strides[3] = {row_b, row_b * op.rows, row_b * op.rows * op.batches};
-    const cuuint32_t box[4] = {32, box_rows, 1, 1};
-    const cuuint32_t estr[4] = {1, 1, 1, 1};
-    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, op.planes, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  kmajor ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-static int pick_bn(const Context &ctx, long long m, long long n, long long batch) {
-    const int cands[4] = {256, 192, 128, 64};
-    int best = 128;
-    double best_cost = 1e300;
-    for (int bn : cands) {
-        if (bn > 64 && n <= bn / 2) continue;  // mostly padding
-        const long long tiles = ((n + bn - 1) / bn) * ((m + BM - 1) / BM) * batch;
-        const long long waves = (tiles + ctx.sm_count - 1) / ctx.sm_count;
-        const double cost = (double)waves * (bn + 24);  // +24: per-tile fixed cost in units of columns
-        if (cost < best_cost) {
-            best_cost = cost;
-            best = bn;
-        }
-    }
-    return best;
-}
-}  // namespace
-
-sage_status gemm_tcgen05(Context &ctx, const GemmArgs &g) {
-    // Tiny problems are latency-bound and would be mostly TMA padding: leave them to the SIMT kernel.
-    if (g.m < 64 || g.n < 32 || g.k < 32 || g.batch < 1) return SAGE_ERR_UNSUPPORTED;
-    if (g.m > 0x7fffffffLL || g.n > 0x7fffffffLL || g.k > 0x7fffffffLL || g.batch > 65535) return SAGE_ERR_UNSUPPORTED;
-    if ((g.m + BM - 1) / BM > 65535) return SAGE_ERR_UNSUPPORTED;
+sage_status gemm_tcgen05_planes(Context &ctx, const GemmArgs &g, const SplitPlanes &a, const SplitPlanes &b) {
     static PFN_encodeTiled encode = nullptr;
     if (!ctx.dry() && !encode) {
         encode = reinterpret_cast<PFN_encodeTiled>(driver_symbol("cuTensorMapEncodeTiled"));
-        if (!encode) return SAGE_ERR_UNSUPPORTED;
+        if (!encode) return ctx.fail(SAGE_ERR_DEVICE, "cuTensorMapEncodeTiled is not available");
     }
     const int bn = pick_bn(ctx, g.m, g.n, g.batch);
     const int stage_bytes = 2 * BM * BK * 4 + 2 * bn * BK * 4;
     int stages = (227 * 1024 - 2048) / stage_bytes;
     if (stages > 4) stages = 4;
     const size_t smem = (size_t)stages * stage_bytes + 1024;
-
-    // A as stored: [M,K] (K-major) or, transposed, [K,M] (MN-major); B: [K,N] (MN-major) or [N,K] (K-major).
-    SplitOperand a, b;
-    sage_status st = split_operand(ctx, g.a, g.lda, g.stride_a, g.ta ? (int)g.k : (int)g.m, g.ta ? (int)g.m : (int)g.k, (int)g.batch, &a);
-    if (st) return st;
-    st = split_operand(ctx, g.b, g.ldb, g.stride_b, g.tb ? (int)g.n : (int)g.k, g.tb ? (int)g.k : (int)g.n, (int)g.batch, &b);
-    if (st) {
-        ctx.allocator().free(a.block);
-        return st;
-    }
     const bool a_kmajor = !g.ta, b_kmajor = g.tb;
     ctx.note_launch("gemm_tc_3xtf32");
-    if (!ctx.dry()) {
-        CUtensorMap map_a, map_b;
-        if (!encode_map(encode, a, a_kmajor ? BM : 32, a_kmajor, &map_a) || !encode_map(encode, b, b_kmajor ? (unsigned)bn : 32, b_kmajor, &map_b)) {
-            ctx.allocator().free(a.block);
-            ctx.allocator().free(b.block);
-            return ctx.fail(SAGE_ERR_DEVICE, "cuTensorMapEncodeTiled failed");
-        }
-        // per device; the limit covers dynamic + static shared memory, so ask for what is used
-        st = ctx.check_cuda(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                            "gemm_tc shared memory attribute");
-        if (st) {
-            ctx.allocator().free(a.block);
-            ctx.allocator().free(b.block);
-            return st;
-        }
-        TcParams p{g.c, g.ldc, g.stride_c, (int)g.m, (int)g.n, (int)g.k, bn, stages, a_kmajor ? 1 : 0, b_kmajor ? 1 : 0, ctx.status_word_dev};
-        dim3 grid((unsigned)((g.n + bn - 1) / bn), (unsigned)((g.m + BM - 1) / BM), (unsigned)g.batch);
-        gemm_tc_kernel<<<grid, kThreads, smem, ctx.stream()>>>(map_a, map_b, p);
-        st = ctx.check_cuda(cudaGetLastError(), "gemm_tc launch");
+    if (ctx.dry()) return SAGE_OK;
+    CUtensorMap map_a, map_b;
+    if (!encode_map(encode, a, a_kmajor ? BM : 32, a_kmajor, &map_a) || !encode_map(encode, b, b_kmajor ? (unsigned)bn : 32, b_kmajor, &map_b))
+        return ctx.fail(SAGE_ERR_DEVICE, "cuTensorMapEncodeTiled failed");
+    TcParams p;
+    p.c = g.c;
+    p.ldc = g.ldc;
+    p.stride_c = g.stride_c;
+    p.m = (int)g.m;
+    p.n = (int)g.n;
+    p.k = (int)g.k;
+    p.stages = stages;
+    p.a_kmajor = a_kmajor;
+    p.b_kmajor = b_kmajor;
+    p.tiles_m = (int)((g.m + BM - 1) / BM);
+    p.tiles_n = (int)((g.n + bn - 1) / bn);
+    p.num_tiles = (int)((long long)p.tiles_m * p.tiles_n * g.batch);
+    p.status = ctx.status_word_dev;
+    const int grid = p.num_tiles < ctx.sm_count ? p.num_tiles : ctx.sm_count;
+    switch (bn) {
+    case 256: return launch_tc<256>(ctx, map_a, map_b, p, grid, smem);
+    case 192: return launch_tc<192>(ctx, map_a, map_b, p, grid, smem);
+    case 128: return launch_tc<128>(ctx, map_a, map_b, p, grid, smem);
+    default: return launch_tc<64>(ctx, map_a, map_b, p, grid, smem);
     }
+}
+
+void free_split(Context &ctx, SplitPlanes *s) {
+    if (s->block) ctx.allocator().free(s->block);
+    s->block = nullptr;
+}
+
+sage_status gemm_tcgen05(Context &ctx, const GemmArgs &g) {
+    if (!gemm_tc_supported(g)) return SAGE_ERR_UNSUPPORTED;
+    // A as stored: [M,K] (K-major) or, transposed, [K,M] (MN-major); B: [K,N] (MN-major) or [N,K] (K-major).
+    SplitPlanes a, b;
+    sage_status st = split_tf32(ctx, g.a, g.lda, g.stride_a, g.ta ? (int)g.k : (int)g.m, g.ta ? (int)g.m : (int)g.k, (int)g.batch, &a);
+    if (st) return st;
+    st = split_tf32(ctx, g.b, g.ldb, g.stride_b, g.tb ? (int)g.n : (int)g.k, g.tb ? (int)g.k : (int)g.n, (int)g.batch, &b);
+    if (!st) st = gemm_tcgen05_planes(ctx, g, a, b);
     // Stream-ordered: the split buffers may be reused by later launches on this stream.
-    ctx.allocator().free(a.block);
-    ctx.allocator().free(b.block);
+    free_split(ctx, &a);
+    free_split(ctx, &b);
     return st;
 }
 

@@ -63,6 +63,19 @@ struct GemmArgs {
     long long ldc, stride_c;
     long long batch;
 };
+// An operand split for 3xTF32: [2 planes (hi, lo)][batches][rows][pitch] floats, rows x cols as the
+// operand lies in memory (cols contiguous), pitch = cols rounded up to 4.
+struct SplitPlanes {
+    Block *block = nullptr;
+    float *planes = nullptr;
+    int rows = 0, cols = 0, pitch = 0, batches = 0;
+};
+bool gemm_tc_supported(const GemmArgs &g);
+sage_status split_tf32(Context &ctx, const float *src, long long ld, long long batch_stride, int rows, int cols, int batches,
+                       SplitPlanes *out);
+void free_split(Context &ctx, SplitPlanes *s);
+// `a` / `b` are the splits of g.a / g.b (as stored); g.a / g.b themselves are not read.
+sage_status gemm_tcgen05_planes(Context &ctx, const GemmArgs &g, const SplitPlanes &a, const SplitPlanes &b);
 sage_status gemm_simt(Context &ctx, const GemmArgs &g);
 // Returns SAGE_ERR_UNSUPPORTED when the shape/alignment cannot go through TMA; the caller
 // then uses gemm_simt.

@@ -1,0 +1,134 @@
+"""Kernel-level micro-benchmarks of the B200 backend: achieved HBM GB/s of the fused map / reduce /
+row kernels and f32-equivalent TFLOP/s of the tensor-core GEMM, each as one JSON line.
+
+  python -m sage_b200.microbench --case gemm --m 4096 --n 768 --k 768 [--batch 1] [--reps 20]
+  python -m sage_b200.microbench --case map --rows 16384 --cols 4096      # z = x*y + x*3.14 (one fused kernel)
+  python -m sage_b200.microbench --case reduce|softmax|layernorm|lse --rows 16384 --cols 4096
+  python -m sage_b200.microbench --case config1 --rows 16384 --cols 4096  # whole forward + grad graph
+  python -m sage_b200.microbench --case all
+
+Times are device times from CUDA events recorded on the context's stream in front of every launch
+(Context.profile_begin / profile_end).  Algorithmic bytes: every distinct input once + the output once.
+"""
+import argparse
+import ctypes
+import json
+import os
+
+import numpy as np
+
+import sage_b200 as S
+
+L = ctypes.c_int64
+
+
+def peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        m = json.load(open(p))
+        return m["hbm_gbs"], m["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def timed(ctx, fn, reps, names):
+    for _ in range(3):
+        fn()
+    ctx.sync()
+    ctx.profile_begin()
+    for _ in range(reps):
+        fn()
+    prof = ctx.profile_end()
+    ms = sum(t for k, (n, t) in prof.items() if any(k.startswith(p) for p in names))
+    return ms / reps, prof
+
+
+def case_gemm(ctx, a):
+    m, n, k, b = a.m, a.n, a.k, a.batch
+    A, B, C = ctx.tensor(np.random.default_rng(0).uniform(-1, 1, (b, m, k)).astype(np.float32)), \
+        ctx.tensor(np.random.default_rng(1).uniform(-1, 1, (b, k, n)).astype(np.float32)), ctx.empty((b, m, n))
+
+    def go():
+        ctx._ck(S.lib.sage_gemm_strided_batched(ctx.h, 0, 0, L(m), L(n), L(k), A.buf, L(0), L(k), L(m * k), B.buf, L(0), L(n), L(k * n),
+                                                C.buf, L(0), L(n), L(m * n), L(b)))
+    ms, prof = timed(ctx, go, a.reps, ["gemm"])
+    split_ms = prof.get("split_tf32", (0, 0.0))[1] / a.reps
+    hbm, bf16, src = peaks()
+    tf = 2.0 * m * n * k * b / (ms * 1e-3) / 1e12
+    return {"case": "gemm", "m": m, "n": n, "k": k, "batch": b, "us": 1e3 * ms, "split_us": 1e3 * split_ms, "tflops_f32_equivalent": tf,
+            "tensor_pipe_tflops": 3 * tf, "peak_bf16_tflops": bf16, "frac_of_bf16_peak": 3 * tf / bf16,
+            "note": "3xTF32: 3 tensor-core MMAs per logical product; TF32 runs at half the bf16 rate, so 1.0 here would be frac 0.5",
+            "peak_source": src, "kernel": [k_ for k_ in prof if k_.startswith("gemm")][0]}
+
+
+def row_case(ctx, a, kind):
+    rows, cols = a.rows, a.cols
+    x = ctx.var(np.random.default_rng(2).standard_normal((rows, cols), dtype=np.float32))
+    if kind == "map":
+        y = ctx.var(np.random.default_rng(3).standard_normal((rows, cols), dtype=np.float32))
+        out, bytes_, names = x * y + x * 3.14, 3 * rows * cols * 4, ["sage_map"]
+    elif kind == "reduce":
+        out, bytes_, names = x.sum([1], True), rows * cols * 4 + rows * 4, ["reduce"]
+    elif kind == "softmax":
+        out, bytes_, names = S.softmax(x, [1]), 2 * rows * cols * 4, ["softmax"]
+    elif kind == "lse":
+        out, bytes_, names = S.log_sum_exp(x, [1]), rows * cols * 4 + rows * 4, ["lse"]
+    else:
+        g, b = ctx.var(np.float32([1.0])), ctx.var(np.float32([0.0]))
+        out, bytes_, names = S.layer_norm(x, [1], g, b, 1e-5), 2 * rows * cols * 4, ["layernorm"]
+
+    def go():
+        ctx.clear()
+        ctx.eval(out)
+    ms, prof = timed(ctx, go, a.reps, names)
+    hbm, _, src = peaks()
+    gbs = bytes_ / (ms * 1e-3) / 1e9
+    return {"case": kind, "rows": rows, "cols": cols, "us": 1e3 * ms, "algorithmic_bytes": bytes_, "gb_per_s": gbs, "peak_hbm_gb_per_s": hbm,
+            "frac": gbs / hbm, "peak_source": src, "kernels": {k: v for k, v in prof.items()}}
+
+
+def case_config1(ctx, a):
+    rows, cols = a.rows, a.cols
+    rng = np.random.default_rng(1001)
+    x, y = ctx.var(rng.standard_normal((rows, cols), dtype=np.float32)), ctx.var(rng.standard_normal((rows, cols), dtype=np.float32))
+    lab = ctx.var(rng.integers(0, cols, (rows, 1)).astype(np.uint32))
+    loss = S.softmax_cross_entropy(x * y + x * 3.14, lab)
+    gx = x.grad(loss)
+
+    def go():
+        ctx.clear()
+        ctx.eval(loss, gx)
+    ms, prof = timed(ctx, go, a.reps, [""])
+    hbm, _, src = peaks()
+    bytes_ = 3 * rows * cols * 4 + rows * 8  # x, y read once, gx written once, labels + loss
+    gbs = bytes_ / (ms * 1e-3) / 1e9
+    return {"case": "config1_fwd_grad", "rows": rows, "cols": cols, "us": 1e3 * ms, "compulsory_bytes": bytes_, "gb_per_s": gbs,
+            "peak_hbm_gb_per_s": hbm, "frac": gbs / hbm, "peak_source": src, "kernels": {k: v for k, v in prof.items()}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default="all")
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=768)
+    ap.add_argument("--k", type=int, default=768)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--rows", type=int, default=16384)
+    ap.add_argument("--cols", type=int, default=4096)
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--device", type=int, default=0)
+    a = ap.parse_args()
+    ctx = S.Context(a.device)
+    cases = ["gemm", "map", "reduce", "softmax", "lse", "layernorm", "config1"] if a.case == "all" else [a.case]
+    for c in cases:
+        if c == "gemm":
+            r = case_gemm(ctx, a)
+        elif c == "config1":
+            r = case_config1(ctx, a)
+        else:
+            r = row_case(ctx, a, c)
+        print(json.dumps(r), flush=True)
+    ctx.close()
+
+
+if __name__ == "__main__":
+    main()

@@ -290,7 +290,12 @@ def test_config1_forward_and_grad(ctx):
 
 # ------------------------------------------------------------------------------ config 2: contractions
 def gemm_err(got, ref):
-    return rel_err(got, ref, floor=1e-3)
+    """Contractions: |a - b| / max(|b|, rms(b)).  An output that cancels to ~0 carries the rounding of
+    K products of ordinary size, so it is measured against the typical output, not against itself."""
+    a, b = np.asarray(got, np.float64), np.asarray(ref, np.float64)
+    assert a.shape == b.shape
+    rms = max(float(np.sqrt((b ** 2).mean())), 1e-30)
+    return float((np.abs(a - b) / np.maximum(np.abs(b), rms)).max())
 
 
 @pytest.mark.parametrize("m,n,k", [(1024, 1024, 1024), (1, 1, 1), (7, 13, 5), (129, 257, 63), (128, 768, 3072), (300, 2, 768)])
