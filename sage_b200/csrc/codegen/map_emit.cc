@@ -69,7 +69,7 @@ static const char *ctype(int dt) { return dt == SAGE_F32 ? "float" : dt == SAGE_
 static const char *vtype(int dt) { return dt == SAGE_F32 ? "float4" : dt == SAGE_I32 ? "int4" : "uint4"; }
 
 sage_status map_plan(const std::string &expr, const std::vector<MapOperand> &in, int out_dtype, const void *y,
-                     int out_ndim, const long long *out_ext, MapPlan *plan) {
+                     int out_ndim, const long long *out_ext, MapPlan *plan, bool emit_source) {
     const int nin = (int)in.size();
     // ---- collapse axes
     long long ext[k::kMaxDims];
@@ -143,6 +143,8 @@ sage_status map_plan(const std::string &expr, const std::vector<MapOperand> &in,
     plan->vec = vec;
     const bool wide = n >= (1LL << 32);
     const char *it = wide ? "unsigned long long" : "unsigned int";
+    plan->signature = modes + ":" + std::to_string(vec) + ":" + std::to_string(nd) + (wide ? "w" : "n");
+    if (!emit_source) return SAGE_OK;  // the caller already holds the kernel for this signature
 
     // ---- emit
     std::ostringstream s;
@@ -210,7 +212,6 @@ sage_status map_plan(const std::string &expr, const std::vector<MapOperand> &in,
     }
     s << "}\n";
     plan->source = s.str();
-    plan->signature = modes + ":" + std::to_string(vec) + ":" + std::to_string(nd) + (wide ? "w" : "n");
     return SAGE_OK;
 }
 
@@ -222,7 +223,7 @@ struct MapPHost {
 sage_status map_launch(Context &ctx, const std::string &expr, const std::vector<MapOperand> &in, int out_dtype,
                        void *y, int out_ndim, const long long *out_ext, MapCache *cache) {
     MapPlan plan;
-    sage_status st = map_plan(expr, in, out_dtype, y, out_ndim, out_ext, &plan);
+    sage_status st = map_plan(expr, in, out_dtype, y, out_ndim, out_ext, &plan, false);
     if (st) return st;
     if (plan.n == 0) return SAGE_OK;
     Module *mod = nullptr;
@@ -231,6 +232,8 @@ sage_status map_launch(Context &ctx, const std::string &expr, const std::vector<
         if (it != cache->by_signature.end()) mod = it->second;
     }
     if (!mod) {
+        st = map_plan(expr, in, out_dtype, y, out_ndim, out_ext, &plan, true);  // first use: write the source
+        if (st) return st;
         st = ctx.module_get(plan.source, &mod);
         if (st) return st;
         if (cache) {
@@ -259,7 +262,13 @@ sage_status map_launch(Context &ctx, const std::string &expr, const std::vector<
     const long long chunks = (plan.n + plan.vec - 1) / plan.vec;
     const uint32_t grid[3] = {(uint32_t)((chunks + 255) / 256), 1, 1};
     const uint32_t block[3] = {256, 1, 1};
-    return ctx.launch(mod, "sage_map", grid, block, 0, params.data());
+    std::string label;
+    if (ctx.verbose_names) {
+        label = "map{" + expr + "}n=" + std::to_string(plan.n) + ",v" + std::to_string(plan.vec) + "," + plan.signature;
+        for (char &ch : label)
+            if (ch == ' ') ch = '_';
+    }
+    return ctx.launch(mod, "sage_map", grid, block, 0, params.data(), label.empty() ? nullptr : label.c_str());
 }
 
 }  // namespace sage

@@ -37,7 +37,7 @@ struct MapPlan {
 // `expr` is a C expression over x0..x{n-1}; helper functions come from the prelude
 // (sg_exp, sg_max, ...).  The output is contiguous with `out_ext`.
 sage_status map_plan(const std::string &expr, const std::vector<MapOperand> &in, int out_dtype, const void *y,
-                     int out_ndim, const long long *out_ext, MapPlan *plan);
+                     int out_ndim, const long long *out_ext, MapPlan *plan, bool emit_source = true);
 
 sage_status map_launch(Context &ctx, const std::string &expr, const std::vector<MapOperand> &in, int out_dtype,
                        void *y, int out_ndim, const long long *out_ext, MapCache *cache);

@@ -39,10 +39,14 @@ void *driver_symbol(const char *name);  // runtime/context.cc
 namespace k {
 
 namespace {
-constexpr int BM = 128, BK = 32;  // BK * 4 bytes = one 128-byte swizzle row
+// A K-block is 32 k wide: K-major tiles are rows of 128 bytes (128-byte swizzle), MN-major tiles are
+// 32 k-rows of 128 bytes.  BK = 16 (64-byte rows, twice the stages) was measured and is slower:
+// the kernel is bound by the bytes each SM can take from L2 (~45 B/clk), not by load latency, and
+// 16-wide K-blocks double the number of TMA operations for the same bytes.
+constexpr int BM = 128, BK = 32;
 constexpr int kThreads = 320;
 constexpr int kEpiWarps = 8;
-constexpr int kChunkKB = 4;       // K-blocks per accumulation chain
+constexpr int kChunkKB = 128 / BK;  // K-blocks per accumulation chain (128 k)
 constexpr long long kTimeoutCycles = 2000000000LL;  // ~1 s
 
 struct TcParams {
@@ -241,8 +245,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // 4 k-rows 512 B apart (stride offset), a k-step (8 k-rows) is 1024 B further.
         const unsigned a_lbo = p.a_kmajor ? 16u : (unsigned)(BK * 128), a_step = p.a_kmajor ? 32u : 1024u;
         const unsigned b_lbo = p.b_kmajor ? 16u : (unsigned)(BK * 128), b_step = p.b_kmajor ? 32u : 1024u;
-        const unsigned a_sbo = p.a_kmajor ? 1024u : 512u, b_sbo = p.b_kmajor ? 1024u : 512u;
-        const unsigned a_lt = p.a_kmajor ? 2u : 1u, b_lt = p.b_kmajor ? 2u : 1u;
+        constexpr unsigned K_SBO = 8u * BK * 4u;           // 8 rows of a K-major tile
+        constexpr unsigned K_LT = BK == 32 ? 2u : 4u;      // 128-byte or 64-byte swizzle
+        const unsigned a_sbo = p.a_kmajor ? K_SBO : 512u, b_sbo = p.b_kmajor ? K_SBO : 512u;
+        const unsigned a_lt = p.a_kmajor ? K_LT : 1u, b_lt = p.b_kmajor ? K_LT : 1u;
         int kbg = 0, cg = 0;  // K-blocks / chunks consumed so far, across tiles
         bool ok = true;
         for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
@@ -388,11 +394,12 @@ bool encode_map(PFN_encodeTiled encode, const SplitPlanes &op, unsigned box_rows
     const cuuint64_t dims[4] = {(cuuint64_t)op.cols, (cuuint64_t)op.rows, (cuuint64_t)op.batches, 2};
     const cuuint64_t row_b = (cuuint64_t)op.pitch * 4;
     const cuuint64_t strides[3] = {row_b, row_b * op.rows, row_b * op.rows * op.batches};
-    const cuuint32_t box[4] = {32, box_rows, 1, 1};
+    // K-major: {BK k, tile rows}; MN-major: {32 mn, BK k-rows}
+    const cuuint32_t box[4] = {kmajor ? (cuuint32_t)BK : 32u, kmajor ? box_rows : (cuuint32_t)BK, 1, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
-    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, op.planes, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  kmajor ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    const CUtensorMapSwizzle sw = !kmajor ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : (BK == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, op.planes, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 int pick_bn(const Context &ctx, long long m, long long n, long long batch) {
@@ -415,9 +422,14 @@ int pick_bn(const Context &ctx, long long m, long long n, long long batch) {
 template <int BN>
 sage_status launch_tc(Context &ctx, const CUtensorMap &map_a, const CUtensorMap &map_b, TcParams p, int grid, size_t smem) {
     // per device; the limit covers dynamic + static shared memory, so ask for what is used
-    sage_status st = ctx.check_cuda(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                                    "gemm_tc shared memory attribute");
-    if (st) return st;
+    static int attr_set[64] = {0};  // per BN instantiation and device
+    const int dev = ctx.device();
+    if (dev < 0 || dev >= 64 || attr_set[dev] != (int)smem) {
+        sage_status st = ctx.check_cuda(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                                        "gemm_tc shared memory attribute");
+        if (st) return st;
+        if (dev >= 0 && dev < 64) attr_set[dev] = (int)smem;
+    }
     gemm_tc_kernel<BN><<<grid, kThreads, smem, ctx.stream()>>>(map_a, map_b, p);
     return ctx.check_cuda(cudaGetLastError(), "gemm_tc launch");
 }
@@ -461,7 +473,7 @@ sage_status gemm_tcgen05_planes(Context &ctx, const GemmArgs &g, const SplitPlan
     const int bn = pick_bn(ctx, g.m, g.n, g.batch);
     const int stage_bytes = 2 * BM * BK * 4 + 2 * bn * BK * 4;
     int stages = (227 * 1024 - 2048) / stage_bytes;
-    if (stages > 4) stages = 4;
+    if (stages > 8) stages = 8;
     const size_t smem = (size_t)stages * stage_bytes + 1024;
     const bool a_kmajor = !g.ta, b_kmajor = g.tb;
     ctx.note_launch("gemm_tc_3xtf32");

@@ -119,6 +119,58 @@ __global__ void __launch_bounds__(256) reduce_kernel(const T *__restrict__ x, T 
     }
 }
 
+// Contiguous reduced run, 16-byte aligned rows: each thread reads 128-bit vectors, four in flight.
+template <typename T, int G>
+__global__ void __launch_bounds__(256) reduce_vec_kernel(const T *__restrict__ x, T *__restrict__ y, RDims outer, long long n_out,
+                                                         long long n_in, int kind, int ref_compat) {
+    struct alignas(16) V4 {
+        T v[4];
+    };
+    __shared__ T smem[8];
+    const int groups_per_block = blockDim.x / G;
+    long long out = (long long)blockIdx.x * groups_per_block + threadIdx.x / G;
+    const int lane = threadIdx.x % G;
+    if (out >= n_out) return;
+    const V4 *base = reinterpret_cast<const V4 *>(x + translate(out, outer));
+    const long long nv = n_in >> 2;
+    T a0 = Ops<T>::identity(kind), a1 = a0, a2 = a0, a3 = a0;
+    long long it = lane;
+    for (; it + 3LL * G < nv; it += 4LL * G) {
+        const V4 p0 = base[it], p1 = base[it + G], p2 = base[it + 2LL * G], p3 = base[it + 3LL * G];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            a0 = Ops<T>::apply(kind, a0, p0.v[j]);
+            a1 = Ops<T>::apply(kind, a1, p1.v[j]);
+            a2 = Ops<T>::apply(kind, a2, p2.v[j]);
+            a3 = Ops<T>::apply(kind, a3, p3.v[j]);
+        }
+    }
+    for (; it < nv; it += G) {
+        const V4 p0 = base[it];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a0 = Ops<T>::apply(kind, a0, p0.v[j]);
+    }
+    T acc = Ops<T>::apply(kind, Ops<T>::apply(kind, a0, a1), Ops<T>::apply(kind, a2, a3));
+    if (G >= 32) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc = Ops<T>::apply(kind, acc, shfl_down_t(acc, off));
+    }
+    if (G == 256) {
+        const int warp = threadIdx.x >> 5;
+        if ((threadIdx.x & 31) == 0) smem[warp] = acc;
+        __syncthreads();
+        if (threadIdx.x < 8) {
+            acc = smem[threadIdx.x];
+#pragma unroll
+            for (int off = 4; off > 0; off >>= 1) acc = Ops<T>::apply(kind, acc, __shfl_down_sync(0xffu, acc, off));
+        }
+    }
+    if (lane == 0) {
+        if (ref_compat) acc = Ops<T>::apply(kind, (T)0, acc);
+        y[out] = acc;
+    }
+}
+
 // Puts the reduced axis with the smallest non-zero stride last (fastest) and merges axes that
 // form one run, so that a group's lanes read neighbouring addresses.  The order of a parallel
 // reduction is free, so this does not change what is computed.
@@ -184,6 +236,16 @@ static sage_status launch_reduce(Context &ctx, int kind, const T *x, const Dims 
     const int compat = ctx.opts().ref_compat;
     ctx.note_launch(G == 1 ? "reduce_g1" : G == 32 ? "reduce_g32" : "reduce_g256");
     if (ctx.dry()) return SAGE_OK;
+    bool vec = G > 1 && inner.ndim == 1 && inner_contig && n_in % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
+    for (int i = 0; i < outer.ndim && vec; ++i)
+        if (outer.ext[i] > 1 && outer.str[i] % 4 != 0) vec = false;
+    if (vec) {
+        if (G == 32)
+            reduce_vec_kernel<T, 32><<<(unsigned)blocks, threads, 0, ctx.stream()>>>(x, y, outer, n_out, n_in, kind, compat);
+        else
+            reduce_vec_kernel<T, 256><<<(unsigned)blocks, threads, 0, ctx.stream()>>>(x, y, outer, n_out, n_in, kind, compat);
+        return ctx.check_cuda(cudaGetLastError(), "reduce launch");
+    }
     if (G == 1)
         reduce_kernel<T, 1><<<(unsigned)blocks, threads, 0, ctx.stream()>>>(x, y, outer, inner, n_out, n_in, kind, compat);
     else if (G == 32)

@@ -134,6 +134,79 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float *smem)
     return r;
 }
 
+// Rows of 2049..16384 elements (multiple of 4): a CTA of 256 threads owns a row and keeps it in
+// registers (V float4 chunks per thread), so HBM still sees one read and one write per element.
+template <int MODE, int V>
+__global__ void __launch_bounds__(256) row_cta_kernel(RowParams p) {
+    __shared__ float smem[8];
+    const long long row = blockIdx.x;
+    const int chunks = (int)(p.cols >> 2);
+    const float4 *xr = reinterpret_cast<const float4 *>(p.x + row * p.cols);
+    float4 v[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const int c = threadIdx.x + 256 * i;
+        if (c < chunks) v[i] = __ldg(xr + c);
+    }
+    if (MODE == ROW_LN) {
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+            if (threadIdx.x + 256 * i < chunks) {
+                s1 += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+                s2 += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+            }
+        s1 = block_reduce(s1, false, smem);
+        s2 = block_reduce(s2, false, smem);
+        const float n = (float)p.cols;
+        const float mean = s1 / n;
+        const float var = s2 / n - mean * mean;
+        const float denom = sqrtf(var + p.eps);
+        float4 *yr = reinterpret_cast<float4 *>(p.y + row * p.cols);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const int c = threadIdx.x + 256 * i;
+            if (c < chunks) {
+                const int e = c * 4;
+                float4 o;
+                o.x = (v[i].x - mean) / denom * p.gamma[(e + 0) * p.gamma_stride] + p.beta[(e + 0) * p.beta_stride];
+                o.y = (v[i].y - mean) / denom * p.gamma[(e + 1) * p.gamma_stride] + p.beta[(e + 1) * p.beta_stride];
+                o.z = (v[i].z - mean) / denom * p.gamma[(e + 2) * p.gamma_stride] + p.beta[(e + 2) * p.beta_stride];
+                o.w = (v[i].w - mean) / denom * p.gamma[(e + 3) * p.gamma_stride] + p.beta[(e + 3) * p.beta_stride];
+                yr[c] = o;
+            }
+        }
+        return;
+    }
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < V; ++i)
+        if (threadIdx.x + 256 * i < chunks) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+    m = block_reduce(m, true, smem);
+    if (p.ref_compat) m = fmaxf(0.f, m);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < V; ++i)
+        if (threadIdx.x + 256 * i < chunks) {
+            v[i].x = expf(v[i].x - m);
+            v[i].y = expf(v[i].y - m);
+            v[i].z = expf(v[i].z - m);
+            v[i].w = expf(v[i].w - m);
+            s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        }
+    s = block_reduce(s, false, smem);
+    if (MODE == ROW_LSE) {
+        if (threadIdx.x == 0) p.y[row] = logf(s) + m;
+        return;
+    }
+    float4 *yr = reinterpret_cast<float4 *>(p.y + row * p.cols);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const int c = threadIdx.x + 256 * i;
+        if (c < chunks) yr[c] = make_float4(v[i].x / s, v[i].y / s, v[i].z / s, v[i].w / s);
+    }
+}
+
 // Any row length: one CTA per row, the row is re-read per pass.
 template <int MODE>
 __global__ void __launch_bounds__(256) row_block_kernel(RowParams p) {
@@ -189,6 +262,13 @@ static sage_status launch_rows(Context &ctx, RowParams p, const char *name) {
         else if (v <= 4) row_warp_kernel<MODE, 4><<<blocks, 256, 0, s>>>(p);
         else if (v <= 8) row_warp_kernel<MODE, 8><<<blocks, 256, 0, s>>>(p);
         else row_warp_kernel<MODE, 16><<<blocks, 256, 0, s>>>(p);
+    } else if (p.cols % 4 == 0 && p.cols <= 16384 && aligned && p.rows < (1LL << 31)) {
+        const int v = (int)((p.cols / 4 + 255) / 256);
+        const unsigned blocks = (unsigned)p.rows;
+        cudaStream_t s = ctx.stream();
+        if (v <= 4) row_cta_kernel<MODE, 4><<<blocks, 256, 0, s>>>(p);
+        else if (v <= 8) row_cta_kernel<MODE, 8><<<blocks, 256, 0, s>>>(p);
+        else row_cta_kernel<MODE, 16><<<blocks, 256, 0, s>>>(p);
     } else {
         row_block_kernel<MODE><<<(unsigned)p.rows, 256, 0, ctx.stream()>>>(p);
     }

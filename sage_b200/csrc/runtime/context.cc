@@ -101,6 +101,7 @@ sage_status Context::create(int device, const sage_ctx_opts &opts, Context **out
     if (const char *e = getenv("SAGE_REF_COMPAT")) c->opts_.ref_compat = atoi(e);
     if (const char *e = getenv("SAGE_PATTERN_FUSION")) c->opts_.pattern_fusion = atoi(e);
     if (const char *e = getenv("SAGE_GEMM_BACKEND")) c->opts_.gemm_backend = atoi(e);
+    if (const char *e = getenv("SAGE_VERBOSE_NAMES")) c->verbose_names = atoi(e) != 0;
     uint64_t cap = opts.mem_capacity_bytes;
     if (const char *e = getenv("SAGE_MEM_CAP")) cap = strtoull(e, nullptr, 10);
     if (device < 0) {
@@ -221,8 +222,8 @@ sage_status Context::module_get(const std::string &src, Module **out) {
 }
 
 sage_status Context::launch(Module *m, const char *name, const uint32_t grid[3], const uint32_t block[3],
-                            uint32_t smem, void **params) {
-    note_launch(name);
+                            uint32_t smem, void **params, const char *label) {
+    note_launch(label && verbose_names ? label : name);
     if (dry()) return SAGE_OK;
     Driver &d = driver();
     CUfunc_st *fn = nullptr;

@@ -115,7 +115,10 @@ public:
 
     sage_status module_get(const std::string &src, Module **out);
     sage_status launch(Module *m, const char *name, const uint32_t grid[3], const uint32_t block[3],
-                       uint32_t smem, void **params);
+                       uint32_t smem, void **params, const char *label = nullptr);
+    // When set, JIT-compiled map kernels are recorded under "map{<expression>}" instead of
+    // "sage_map" in traces and profiles (more names, same launches).
+    bool verbose_names = false;
 
     // bookkeeping for every kernel the library launches itself (static kernels call note_launch)
     void note_launch(const char *name) {
