@@ -202,6 +202,23 @@ sage_status sage_gemm_strided_batched(sage_ctx *ctx, int32_t trans_a, int32_t tr
                                       const sage_buf *b, int64_t b_off, int64_t ldb, int64_t stride_b,
                                       sage_buf *c, int64_t c_off, int64_t ldc, int64_t stride_c, int64_t batch);
 
+/* No counterpart in the reference (which allocates a fresh buffer in every compute()).
+ * The same tensor-core GEMM as sage_gemm for callers that may not allocate device memory —
+ * a host whose HBM was partitioned in advance by another runtime, or a latency-critical loop
+ * that must not meet cudaMalloc's device-wide synchronisation.  The hi/lo operand split goes
+ * into a fixed 32 MiB array inside the library's device image instead of the context's
+ * allocator, and the call performs no cudaMalloc / cudaFree / pool allocation at all.
+ * Limits: m >= 64, n >= 32, k >= 32, and 8 bytes x (rows_a x pitch(cols_a) + rows_b x pitch(cols_b))
+ * <= 32 MiB (pitch = contiguous extent rounded up to 4); otherwise SAGE_ERR_UNSUPPORTED /
+ * SAGE_ERR_INVALID with a message naming the limit.  The first call on a device resolves the
+ * array's address; make it before any stream capture.  All calls share the array (it keeps the
+ * previous call's contents; every byte a call reads is rewritten by that call first), so calls
+ * that overlap on one GPU race and must be serialised by the caller. */
+sage_status sage_gemm_noalloc(sage_ctx *ctx, int32_t trans_a, int32_t trans_b, int64_t m, int64_t n, int64_t k,
+                              const sage_buf *a, int64_t a_off, int64_t lda,
+                              const sage_buf *b, int64_t b_off, int64_t ldb,
+                              sage_buf *c, int64_t c_off, int64_t ldc);
+
 typedef struct {
     /* every pair is ordered [w, h] like the reference's SizedExtent<2> arguments
      * (src/ops/conv.rs:83,205-209,359-368) */

@@ -464,6 +464,31 @@ sage_status split_tf32(Context &ctx, const float *src, long long ld, long long b
     return ctx.check_cuda(cudaGetLastError(), "split_tf32 launch");
 }
 
+// Same split, written into memory the caller provides (`dst` must hold split_tf32_bytes(...) bytes
+// and be 16-byte aligned).  Nothing is allocated; out->block stays null.
+size_t split_tf32_bytes(int rows, int cols, int batches) {
+    return (size_t)batches * rows * ((cols + 3) / 4 * 4) * 2 * sizeof(float);
+}
+
+sage_status split_tf32_into(Context &ctx, const float *src, long long ld, long long batch_stride, int rows, int cols, int batches,
+                            float *dst, SplitPlanes *out) {
+    out->block = nullptr;
+    out->planes = dst;
+    out->rows = rows;
+    out->cols = cols;
+    out->batches = batches;
+    out->pitch = (cols + 3) / 4 * 4;
+    const size_t plane = (size_t)batches * rows * out->pitch;
+    ctx.note_launch("split_tf32");
+    if (ctx.dry()) return SAGE_OK;
+    const long long total = (long long)plane / 4;
+    long long blocks = (total + 255) / 256;
+    const long long cap = (long long)ctx.sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    split_tf32_kernel<<<(unsigned)blocks, 256, 0, ctx.stream()>>>(src, ld, batch_stride, rows, cols, batches, dst, out->pitch, (long long)plane);
+    return ctx.check_cuda(cudaGetLastError(), "split_tf32 launch");
+}
+
 sage_status gemm_tcgen05_planes(Context &ctx, const GemmArgs &g, const SplitPlanes &a, const SplitPlanes &b) {
     static PFN_encodeTiled encode = nullptr;
     if (!ctx.dry() && !encode) {

@@ -74,6 +74,10 @@ bool gemm_tc_supported(const GemmArgs &g);
 sage_status split_tf32(Context &ctx, const float *src, long long ld, long long batch_stride, int rows, int cols, int batches,
                        SplitPlanes *out);
 void free_split(Context &ctx, SplitPlanes *s);
+// The same split into caller-provided device memory of split_tf32_bytes(...) bytes; allocates nothing.
+size_t split_tf32_bytes(int rows, int cols, int batches);
+sage_status split_tf32_into(Context &ctx, const float *src, long long ld, long long batch_stride, int rows, int cols, int batches,
+                            float *dst, SplitPlanes *out);
 // `a` / `b` are the splits of g.a / g.b (as stored); g.a / g.b themselves are not read.
 sage_status gemm_tcgen05_planes(Context &ctx, const GemmArgs &g, const SplitPlanes &a, const SplitPlanes &b);
 sage_status gemm_simt(Context &ctx, const GemmArgs &g);
