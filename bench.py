@@ -33,6 +33,10 @@ CFG = dict(embed_dim=768, num_vocabs=30522, max_num_tokens=512, hidden_dim=3072,
 METRIC, UNIT = "bert_base_fwd_seq_per_s", "seq/s"
 
 
+WORKLOAD = ("sage models::Bert BertConfig::base() forward (12 layers, hidden 768, 12 heads, FFN 3072, ReLU, "
+            "LayerNorm eps 1e-5, vocab 30522), seq 128, f32, random N(0,0.02) weights")
+
+
 def gemm_flops(batch, seq, c=CFG):
     """Logical 2*M*N*K of every contraction in one forward pass."""
     t, e, f, h = batch * seq, c["embed_dim"], c["hidden_dim"], c["num_heads"]
@@ -143,7 +147,8 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * el / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "sage models::Bert BertConfig::base() forward, seq 128, f32", "batch_per_step": sample_batch},
+        "config": {"workload": WORKLOAD, "batch_per_gpu": BATCH, "global_batch": BATCH, "seq_len": SEQ,
+                   "sample_batch_per_step": sample_batch},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cpu.cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -153,7 +158,7 @@ def run_reference(args, rank, world):
 # ------------------------------------------------------------------------------ GPU arm
 def run_ours(args, rank, local_rank, world, dist):
     import sage_b200 as S  # raises if libsagecuda.so is missing: there is no fallback
-    from sage_b200.shard import OutputGather
+    from sage_b200.shard import OutputGather, max_over_ranks
 
     if S.device_count() <= local_rank:
         raise RuntimeError("bench.py needs CUDA device %d; there is no CPU fallback" % local_rank)
@@ -225,11 +230,7 @@ def run_ours(args, rank, local_rank, world, dist):
     e2e_s = time.perf_counter() - t0
     barrier()
 
-    if world > 1:
-        import torch
-        t = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device="cuda:%d" % local_rank)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_s = float(t[0]), float(t[1]) / 1e3
+    ms, e2e_s = max_over_ranks(dist, world, [ms, e2e_s], device="cuda:%d" % local_rank)
     gathered_ok = None
     if rank == 0:
         g = gather.read((BATCH * world, CFG["num_classes"]))
@@ -292,8 +293,7 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": r["ms"] / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "sage models::Bert BertConfig::base() forward (12 layers, hidden 768, 12 heads, FFN 3072, ReLU, "
-                               "LayerNorm eps 1e-5, vocab 30522), seq 128, f32, random N(0,0.02) weights",
+        "config": {"workload": WORKLOAD,
                    "batch_per_gpu": BATCH, "global_batch": BATCH * world, "seq_len": SEQ, "parallelism": "batch-sharded x%d, weight replicas" % world,
                    "l2": "weights (436 MB) + activations exceed the 126 MB L2; no explicit flush"},
         "clocks": r["clocks"],

@@ -24,6 +24,24 @@ def row_offsets(global_batch, world, row_bytes):
     return [batch_slice(global_batch, r, world)[0] * row_bytes for r in range(world)]
 
 
+def share_from_rank0(dist, world, payload):
+    """Rank 0's `payload` (any picklable object) on every rank; a no-op for one rank."""
+    box = [payload]
+    if world > 1:
+        dist.broadcast_object_list(box, src=0)
+    return box[0]
+
+
+def max_over_ranks(dist, world, values, device=None):
+    """Element-wise maximum of a list of floats over all ranks (the slowest rank sets the time)."""
+    if world <= 1:
+        return [float(v) for v in values]
+    import torch
+    t = torch.tensor(list(values), dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t.cpu()]
+
+
 class OutputGather:
     """Rank 0 owns `global_rows * row_bytes` bytes; every rank writes its rows into it."""
 
@@ -33,22 +51,21 @@ class OutputGather:
         self.row_bytes, self.global_rows = row_bytes, global_rows
         self.offsets = row_offsets(global_rows, world, row_bytes)
         self.buf = None
-        payload = [None]
+        payload = None
         if rank == 0:
             self.buf = ctx.alloc(global_rows * row_bytes)
             handle = (ctypes.c_uint8 * 64)()
             off = ctypes.c_uint64(0)
             ctx._ck(lib.sage_ipc_export(ctx.h, self.buf, handle, ctypes.byref(off)))
-            payload = [(bytes(handle), off.value)]
+            payload = (bytes(handle), off.value)
             self.base = lib.sage_buf_ptr(self.buf)
             self.base_off = 0
-        if world > 1:
-            dist.broadcast_object_list(payload, src=0)
+        payload = share_from_rank0(dist, world, payload)
         if rank != 0:
-            handle = (ctypes.c_uint8 * 64).from_buffer_copy(payload[0][0])
+            handle = (ctypes.c_uint8 * 64).from_buffer_copy(payload[0])
             p = _P()
             ctx._ck(lib.sage_ipc_open(ctx.h, handle, ctypes.byref(p)))
-            self.base, self.base_off = p.value, payload[0][1]
+            self.base, self.base_off = p.value, payload[1]
 
     def write(self, session_var):
         """Asynchronously copies this rank's evaluated output into its rows of rank 0's buffer."""
