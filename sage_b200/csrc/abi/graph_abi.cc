@@ -108,7 +108,7 @@ sage_status sage_var_set(sage_session *s, sage_var *v, const void *data, int32_t
             if (st) return st;
             cur = t;
         }
-        cur.data->split.reset();  // the buffer is being rewritten: any cached tf32 split is stale
+        cur.data->drop_splits();  // the buffer is being rewritten: any cached tf32 split is stale
         return upload_into(C, &cur, data, async != 0);
     });
 }

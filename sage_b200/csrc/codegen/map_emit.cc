@@ -65,6 +65,8 @@ SG uint sg_max(uint a, uint b) { return a > b ? a : b; }
 SG float sg_lit(uint bits) { return __uint_as_float(bits); }
 )";
 
+const char *map_prelude_text() { return kPrelude; }
+
 static const char *ctype(int dt) { return dt == SAGE_F32 ? "float" : dt == SAGE_I32 ? "int" : "uint"; }
 static const char *vtype(int dt) { return dt == SAGE_F32 ? "float4" : dt == SAGE_I32 ? "int4" : "uint4"; }
 

@@ -64,17 +64,27 @@ struct TensorDesc {
 // Device memory returns to the allocator when the last handle drops (OpenClMemory, memory.rs:672-692).
 // The tf32 hi/lo split of (a view of) a storage, kept next to it so that weights and activations
 // read by several GEMMs are split once.  Dropped with the storage, or when the storage is rewritten.
+// Two forms: `whole` planes mirror the storage element for element (hi at planes.planes[i], lo
+// `plane` floats further), so any view of the storage is the same view of the planes; a compact
+// split holds one strided view gathered into rows with a 16-byte pitch.
 struct SplitCache {
     k::SplitPlanes planes;
     std::shared_ptr<Allocator> alloc;
-    long long offset = 0, ld = 0, batch_stride = 0;  // the view that was split
+    bool whole = false;
+    long long plane = 0;     // whole: floats between the hi and the lo plane
+    Shape view;              // compact: the view that was gathered
     ~SplitCache() {
         if (alloc && planes.block) alloc->free(planes.block);
     }
 };
 
 struct Storage {
-    std::shared_ptr<SplitCache> split;
+    std::shared_ptr<SplitCache> split;       // whole-storage planes
+    std::shared_ptr<SplitCache> split_view;  // last compact split of a view
+    void drop_splits() {
+        split.reset();
+        split_view.reset();
+    }
     Context *ctx = nullptr;  // identity only; never dereferenced by the destructor
     std::shared_ptr<Allocator> alloc;
     Block *block = nullptr;

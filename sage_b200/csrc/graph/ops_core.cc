@@ -64,6 +64,12 @@ struct ViewOp : Operator {
     }
 };
 
+bool is_view_op(const Operator &op) { return dynamic_cast<const ViewOp *>(&op) != nullptr; }
+bool is_reshape_op(const Operator &op) {
+    const ViewOp *v = dynamic_cast<const ViewOp *>(&op);
+    return v && v->kind == VReshape;
+}
+
 bool is_expand_op(const Operator &op) {
     const ViewOp *v = dynamic_cast<const ViewOp *>(&op);
     return v && v->kind == VExpand;

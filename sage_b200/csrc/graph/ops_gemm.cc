@@ -1,19 +1,185 @@
 // Matrix products.  Reference: src/ops/gemm.rs — matmul :30-51, matmul_batched :53-104, gemm
 // :106-140, Gemm::compute_direct :176-250, gemm_batched :253-290, GemmBatched::compute_direct
-// :338-421.  Operands are forced contiguous by organize(), so the leading dimension is the row
-// length; C is row-major [M,N].  The reference zero-fills C before the kernel (gemm.rs:179); with
-// beta = 0 that fill has no effect on the result and is dropped here.
+// :338-421.  As in the reference the graph forces operands contiguous with organize() and C is
+// row-major [M,N]; the reference zero-fills C before the kernel (gemm.rs:179), which has no effect
+// with beta = 0 and is dropped here.
+//
+// What the evaluator may change when it lowers a routine (session.cc; the graph that grad() sees is
+// never touched):
+//   * an operand that is an organize() copy of a strided view (head split, transposed keys) is read
+//     through the view itself: TMA addresses the view, the copy kernel disappears;
+//   * the elementwise map that consumes the product (bias, residual, scale + mask, relu ...) becomes
+//     the GEMM's epilogue expression;
+//   * a permuted copy of the product (head merge) becomes the GEMM's store pattern;
+//   * the product's tf32 hi/lo planes are written by the epilogue when another GEMM reads it next.
 #include "graph.h"
 
 namespace sage {
 using namespace ops;
 
+// ------------------------------------------------------------------------------ tf32 planes of a storage
+sage_status storage_planes_attach(Context &ctx, Storage &st) {  // allocate only; the caller's kernel fills them
+    if (st.split) return SAGE_OK;
+    auto c = std::make_shared<SplitCache>();
+    c->alloc = ctx.allocator_ptr();
+    c->whole = true;
+    const size_t bytes = (st.bytes + 511) / 512 * 512;
+    c->plane = (long long)(bytes / 4);
+    c->planes.block = ctx.allocator().alloc(2 * bytes);
+    if (!c->planes.block) return ctx.fail(SAGE_ERR_OOM, "out of memory for tf32 planes");
+    c->planes.planes = reinterpret_cast<float *>(c->planes.block->ptr);
+    st.split = c;
+    return SAGE_OK;
+}
+
+static sage_status storage_planes(Context &ctx, Storage &st) {  // planes of existing data: run the split pass
+    if (st.split) return SAGE_OK;
+    sage_status s = storage_planes_attach(ctx, st);
+    if (s) return s;
+    s = k::split_tf32_flat(ctx, (const float *)st.dev, (long long)(st.bytes / 4), st.split->planes.planes, st.split->plane);
+    if (s) st.split.reset();
+    return s;
+}
+
+// ------------------------------------------------------------------------------ operand views
+// A GEMM operand is a tensor view of rank >= 2: the last two axes are the matrix, the axes before
+// them the batch.  `levels` collapses the batch axes into at most two (extent, stride) pairs,
+// innermost first; false when that is not possible.
+struct BatchLevels {
+    long long n[2] = {1, 1}, s[2] = {0, 0};
+};
+static bool collapse_batch(const Shape &sh, int nbatch_axes, BatchLevels *out) {
+    std::vector<std::pair<long long, long long>> lv;  // outermost first
+    for (int i = 0; i < nbatch_axes; ++i) {
+        const long long e = sh.extents[i], s = sh.strides[i];
+        if (e == 1) continue;
+        if (!lv.empty() && lv.back().second == s * e) lv.back() = {lv.back().first * e, s};
+        else lv.push_back({e, s});
+    }
+    if (lv.size() > 2) return false;
+    *out = BatchLevels();
+    if (lv.size() == 1) {
+        out->n[0] = lv[0].first;
+        out->s[0] = lv[0].second;
+    } else if (lv.size() == 2) {
+        out->n[1] = lv[0].first;
+        out->s[1] = lv[0].second;
+        out->n[0] = lv[1].first;
+        out->s[0] = lv[1].second;
+    }
+    return true;
+}
+
+// Can TMA read this view straight from whole-storage planes?  `swapped` = the row axis is the
+// contiguous one (the matrix lies transposed in memory).
+static bool view_direct(const Shape &sh, bool *swapped, BatchLevels *bl) {
+    const int r = sh.rank();
+    if (r < 2 || !collapse_batch(sh, r - 2, bl)) return false;
+    const long long R = sh.extents[r - 2], C = sh.extents[r - 1], sR = sh.strides[r - 2], sC = sh.strides[r - 1];
+    long long ld;
+    if (sC == 1 || C == 1) {
+        *swapped = false;
+        ld = R == 1 ? (C + 3) / 4 * 4 : sR;
+    } else if (sR == 1 || R == 1) {
+        *swapped = true;
+        ld = sC;
+    } else {
+        return false;
+    }
+    if (ld <= 0 || ld % 4 || sh.offset % 4) return false;
+    for (int l = 0; l < 2; ++l)
+        if (bl->n[l] > 1 && (bl->s[l] <= 0 || bl->s[l] % 4)) return false;
+    return true;
+}
+
+bool gemm_operand_view_ok(const Shape &sh) {
+    bool sw;
+    BatchLevels bl;
+    return view_direct(sh, &sw, &bl);
+}
+
+// Fills `op` for tensor `t`; *swapped tells whether the matrix lies transposed in memory.  Keeps the
+// planes alive through *hold.
+static sage_status make_operand(Context &ctx, const Tensor &t, k::TcOperand *op, bool *swapped, std::shared_ptr<SplitCache> *hold) {
+    const Shape &sh = t.desc.shape;
+    const int r = sh.rank();
+    BatchLevels bl;
+    Storage &st = *t.data;
+    // A view that covers a small part of a large allocation is gathered instead of splitting it all.
+    const bool small_part = !st.split && (unsigned long long)sh.size() * 16 < st.bytes;
+    if (view_direct(sh, swapped, &bl) && !small_part) {
+        sage_status s = storage_planes(ctx, st);
+        if (s) return s;
+        *hold = st.split;
+        const long long R = sh.extents[r - 2], C = sh.extents[r - 1];
+        op->hi = st.split->planes.planes + sh.offset;
+        op->plane = st.split->plane;
+        op->rows = *swapped ? C : R;
+        op->cols = *swapped ? R : C;
+        op->ld = *swapped ? sh.strides[r - 1] : (R == 1 ? (C + 3) / 4 * 4 : sh.strides[r - 2]);
+        if (op->rows == 1) op->ld = (op->cols + 3) / 4 * 4;
+        op->nb0 = bl.n[0];
+        op->nb1 = bl.n[1];
+        op->sb0 = bl.s[0];
+        op->sb1 = bl.s[1];
+        return SAGE_OK;
+    }
+    // Gather the view into compact planes (any strides; one pass instead of organize() + split).
+    if (!collapse_batch(sh, r - 2, &bl)) return ctx.fail(SAGE_ERR_UNSUPPORTED, "gemm: batch axes of an operand do not collapse to two levels");
+    *swapped = false;
+    std::shared_ptr<SplitCache> &c = st.split_view;
+    if (!(c && c->view == sh)) {
+        auto fresh = std::make_shared<SplitCache>();
+        fresh->alloc = ctx.allocator_ptr();
+        fresh->view = sh;
+        k::SplitView v;
+        v.nb0 = bl.n[0];
+        v.nb1 = bl.n[1];
+        v.sb0 = bl.s[0];
+        v.sb1 = bl.s[1];
+        v.rows = sh.extents[r - 2];
+        v.cols = sh.extents[r - 1];
+        v.ld = sh.strides[r - 2];
+        v.col_stride = sh.strides[r - 1];
+        sage_status s = k::split_tf32_view(ctx, (const float *)t.ptr(), v, &fresh->planes);
+        if (s) return s;
+        c = fresh;
+    }
+    *hold = c;
+    const k::SplitPlanes &p = c->planes;
+    op->hi = p.planes;
+    op->ld = p.pitch;
+    op->rows = p.rows;
+    op->cols = p.cols;
+    op->nb0 = p.batches;
+    op->nb1 = 1;
+    op->sb0 = (long long)p.rows * p.pitch;
+    op->sb1 = 0;
+    op->plane = (long long)p.batches * p.rows * p.pitch;
+    return SAGE_OK;
+}
+
+// ------------------------------------------------------------------------------ the operator
+// Axis groups of the epilogue's index space.
+enum { GBatchHi = 0, GBatchLo = 1, GRow = 2, GCol = 3 };
+
 struct GemmOp : Operator {
-    bool ta, tb, batched;
+    bool ta = false, tb = false, batched = false;
+    // ---- set by the evaluator's lowering; the defaults describe the plain operator
+    bool lowered = false;           // operands are views [batch axes..., rows, cols]; m/n/k/batch below are valid
+    long long m = 0, n = 0, k = 0, batch = 1;
+    std::string epilogue;           // C expression over x0 (the product) and x1.. (inputs 2..)
+    Array epi_ext;                  // extents of the epilogue operands (the fused map's index space)
+    std::vector<int> epi_group;     // per axis of epi_ext: GBatchHi .. GCol
+    bool folded = false;            // result stored through (ldc, sc0, sc1, nbc0) instead of row-major [batch, M, N]
+    long long ldc = 0, sc0 = 0, sc1 = 0, nbc0 = 1;
+
     const char *name() const override { return batched ? "gemm_batched" : "gemm"; }
     Cat cat() const override { return Cat::Contract; }
+    int naux() const { return (int)in.size() - 2; }
 
     std::vector<Var> grad(const std::vector<Var> &x, const Var &, const Var &gy) override {  // gemm.rs:150-163,304-328
+        if (lowered) shape_fail("a lowered gemm is not differentiated");
         auto g = [&](const Var &a, const Var &b, bool t1, bool t2) { return batched ? gemm_batched(a, b, t1, t2) : gemm(a, b, t1, t2); };
         if (!ta && !tb) return {g(gy, x[1], false, true), g(x[0], gy, true, false)};
         if (!ta && tb) return {g(gy, x[1], false, false), g(gy, x[0], true, false)};
@@ -21,60 +187,294 @@ struct GemmOp : Operator {
         return {g(x[1], gy, true, true), g(gy, x[0], true, true)};
     }
 
-    sage_status compute(const std::vector<Tensor> &x, Context &ctx, Tensor *y) override {
-        sage_status st = Tensor::uninit(ctx, out, y);
-        if (st) return st;
-        const int o = batched ? 1 : 0;
-        const Shape &a = x[0].desc.shape, &b = x[1].desc.shape;
-        const int h_ax = ta ? 1 : 0, c_ax = ta ? 0 : 1, w_ax = tb ? 0 : 1;
-        k::GemmArgs g;
-        g.ta = ta;
-        g.tb = tb;
-        g.m = a.extents[h_ax + o];
-        g.k = a.extents[c_ax + o];
-        g.n = b.extents[w_ax + o];
-        g.a = (const float *)x[0].ptr();
-        g.b = (const float *)x[1].ptr();
-        g.c = (float *)y->ptr();
-        g.lda = a.strides[o];
-        g.ldb = b.strides[o];
-        g.ldc = g.n;
-        g.batch = batched ? a.extents[0] : 1;
-        g.stride_a = batched ? a.strides[0] : 0;
-        g.stride_b = batched ? b.strides[0] : 0;
-        g.stride_c = g.m * g.n;
-        if (ctx.opts().gemm_backend == 1 || !k::gemm_tc_supported(g)) return k::gemm_simt(ctx, g);
-        // Tensor-core path: each operand's hi/lo split is cached on its storage.
-        std::shared_ptr<SplitCache> sa, sb;
-        st = split_of(ctx, x[0], g.lda, g.stride_a, ta ? g.k : g.m, ta ? g.m : g.k, g.batch, &sa);
-        if (st) return st;
-        st = split_of(ctx, x[1], g.ldb, g.stride_b, tb ? g.n : g.k, tb ? g.k : g.n, g.batch, &sb);
-        if (st) return st;
-        return k::gemm_tcgen05_planes(ctx, g, sa->planes, sb->planes);
+    void dims_from_inputs() {  // m, n, k, batch from in[0] / in[1] (last two axes = matrix)
+        const Shape &a = in[0].shape, &b = in[1].shape;
+        const int ra = a.rank(), rb = b.rank();
+        m = ta ? a.extents[ra - 1] : a.extents[ra - 2];
+        k = ta ? a.extents[ra - 2] : a.extents[ra - 1];
+        n = tb ? b.extents[rb - 2] : b.extents[rb - 1];
+        batch = 1;
+        for (int i = 0; i < ra - 2; ++i) batch *= a.extents[i];
     }
 
-    static sage_status split_of(Context &ctx, const Tensor &t, long long ld, long long batch_stride, long long rows, long long cols,
-                                long long batches, std::shared_ptr<SplitCache> *out) {
-        std::shared_ptr<SplitCache> &c = t.data->split;
-        const long long off = t.desc.shape.offset;
-        if (c && c->offset == off && c->ld == ld && c->batch_stride == batch_stride && c->planes.rows == rows && c->planes.cols == cols &&
-            c->planes.batches == batches) {
-            *out = c;
-            return SAGE_OK;
-        }
-        auto fresh = std::make_shared<SplitCache>();
-        fresh->alloc = ctx.allocator_ptr();
-        fresh->offset = off;
-        fresh->ld = ld;
-        fresh->batch_stride = batch_stride;
-        sage_status st = k::split_tf32(ctx, (const float *)t.ptr(), ld, batch_stride, (int)rows, (int)cols, (int)batches, &fresh->planes);
+    sage_status compute(const std::vector<Tensor> &x, Context &ctx, Tensor *y) override {
+        const bool emit = ctx.hint_emit_planes;
+        ctx.hint_emit_planes = false;
+        sage_status st = Tensor::uninit(ctx, out, y);
         if (st) return st;
-        c = fresh;
-        *out = fresh;
-        return SAGE_OK;
+        if (!lowered) dims_from_inputs();
+        if (!lowered && (ctx.opts().gemm_backend == 1 || !k::gemm_tc_shape_ok(m, n, k, batch))) {
+            const int o = batched ? 1 : 0;
+            const Shape &a = x[0].desc.shape, &b = x[1].desc.shape;
+            k::GemmArgs g;
+            g.ta = ta;
+            g.tb = tb;
+            g.m = m;
+            g.k = k;
+            g.n = n;
+            g.a = (const float *)x[0].ptr();
+            g.b = (const float *)x[1].ptr();
+            g.c = (float *)y->ptr();
+            g.lda = a.strides[o];
+            g.ldb = b.strides[o];
+            g.ldc = n;
+            g.batch = batch;
+            g.stride_a = batched ? a.strides[0] : 0;
+            g.stride_b = batched ? b.strides[0] : 0;
+            g.stride_c = m * n;
+            return k::gemm_simt(ctx, g);
+        }
+        k::TcGemm g;
+        g.m = m;
+        g.n = n;
+        g.k = k;
+        g.batch = batch;
+        std::shared_ptr<SplitCache> hold_a, hold_b;
+        bool sw_a = false, sw_b = false;
+        st = make_operand(ctx, x[0], &g.a, &sw_a, &hold_a);
+        if (st) return st;
+        st = make_operand(ctx, x[1], &g.b, &sw_b, &hold_b);
+        if (st) return st;
+        // A lies as [M,K] (K contiguous) unless transposed; B as [K,N] (N contiguous) unless transposed.
+        g.a_kmajor = (!ta) != sw_a;
+        g.b_kmajor = tb != sw_b;
+        if (g.a.nb0 * g.a.nb1 != batch || g.b.nb0 * g.b.nb1 != batch) {
+            // a batch of one on one side (or levels merged differently) still addresses every batch
+            if (g.a.nb0 * g.a.nb1 != batch || g.b.nb0 * g.b.nb1 != batch)
+                return ctx.fail(SAGE_ERR_INVALID, "gemm: operand batch extents differ from the operator's");
+        }
+        g.c = (float *)y->ptr();
+        if (folded) {
+            g.ldc = ldc;
+            g.sc0 = sc0;
+            g.sc1 = sc1;
+            g.nbc0 = nbc0;
+        } else {
+            g.ldc = n;
+            g.sc0 = m * n;
+            g.sc1 = 0;
+            g.nbc0 = batch;
+        }
+        if (emit) {
+            st = storage_planes_attach(ctx, *y->data);
+            if (st) return st;
+            g.c_hi = y->data->split->planes.planes + y->desc.shape.offset;
+            g.c_plane = y->data->split->plane;
+        }
+        g.naux = naux();
+        g.epilogue = epilogue;
+        // the epilogue's batch decomposition: the axes of epi_ext tagged batch low / high
+        long long e_nb0 = batch;
+        if (g.naux > 0) {
+            e_nb0 = 1;
+            bool any_hi = false;
+            for (size_t d = 0; d < epi_ext.size(); ++d) {
+                if (epi_group[d] == GBatchLo) e_nb0 *= epi_ext[d];
+                if (epi_group[d] == GBatchHi && epi_ext[d] > 1) any_hi = true;
+            }
+            if (!any_hi && e_nb0 != batch) return ctx.fail(SAGE_ERR_INVALID, "internal: gemm epilogue batch groups do not cover the batch");
+            if (folded && nbc0 != e_nb0 && batch > 1) return ctx.fail(SAGE_ERR_INVALID, "internal: gemm epilogue and store pattern split the batch differently");
+            if (!folded) g.nbc0 = e_nb0, g.sc0 = m * n, g.sc1 = m * n * e_nb0;
+        }
+        for (int i = 0; i < g.naux; ++i) {
+            const Tensor &t = x[2 + i];
+            const Shape &sh = t.desc.shape;
+            if (sh.extents != epi_ext) return ctx.fail(SAGE_ERR_INVALID, "internal: gemm epilogue operand extents changed");
+            long long gs[4] = {0, 0, 0, 0};
+            bool seen[4] = {false, false, false, false};
+            for (int d = (int)epi_ext.size() - 1; d >= 0; --d) {  // innermost axis of each group gives its stride
+                if (epi_ext[d] == 1) continue;
+                const int grp = epi_group[d];
+                if (!seen[grp]) {
+                    seen[grp] = true;
+                    gs[grp] = sh.strides[d];
+                }
+            }
+            if (!epilogue_operand_ok(sh, epi_ext, epi_group)) return ctx.fail(SAGE_ERR_INVALID, "internal: gemm epilogue operand is not addressable");
+            g.aux[i].ptr = (const float *)t.ptr();
+            g.aux[i].s1 = gs[GBatchHi];
+            g.aux[i].s0 = gs[GBatchLo];
+            g.aux[i].sr = gs[GRow];
+            g.aux[i].sc = (int)gs[GCol];
+        }
+        return k::gemm_tc_run(ctx, g);
+    }
+
+    // Each group's axes must step through the operand like one axis (or not at all), and the
+    // column group with stride 0 or 1.
+    static bool epilogue_operand_ok(const Shape &sh, const Array &ext, const std::vector<int> &group) {
+        for (int grp = 0; grp < 4; ++grp) {
+            long long inner_stride = 0, span = 1;
+            bool first = true;
+            for (int d = (int)ext.size() - 1; d >= 0; --d) {
+                if (group[d] != grp || ext[d] == 1) continue;
+                if (first) {
+                    inner_stride = sh.strides[d];
+                    first = false;
+                } else if (sh.strides[d] != inner_stride * span) {
+                    return false;
+                }
+                span *= ext[d];
+            }
+            if (grp == GCol && inner_stride != 0 && inner_stride != 1) return false;
+            if (inner_stride < 0) return false;
+        }
+        return true;
     }
 };
 
+// ------------------------------------------------------------------------------ lowering helpers (used by session.cc)
+static const GemmOp *as_gemm(const Operator &op) { return dynamic_cast<const GemmOp *>(&op); }
+
+bool gemm_runs_on_tc(const Operator &op, bool tc_enabled) {
+    const GemmOp *g = as_gemm(op);
+    if (!g || !tc_enabled) return false;
+    if (g->lowered) return true;
+    GemmOp probe = *g;
+    probe.dims_from_inputs();
+    return k::gemm_tc_shape_ok(probe.m, probe.n, probe.k, probe.batch);
+}
+
+// A GEMM that runs on the tensor cores and has not been given an epilogue or a store pattern yet.
+bool gemm_can_fuse(const Operator &op, bool tc_enabled) {
+    const GemmOp *g = as_gemm(op);
+    return g && g->epilogue.empty() && !g->folded && g->naux() == 0 && gemm_runs_on_tc(op, tc_enabled);
+}
+
+static std::shared_ptr<GemmOp> lowered_clone(const GemmOp &g) {
+    auto c = std::make_shared<GemmOp>(g);
+    if (!c->lowered) {
+        c->dims_from_inputs();
+        c->lowered = true;
+    }
+    return c;
+}
+
+// Operand `idx` (0 or 1) read through `view` (rank >= 2: batch axes, then the matrix as organize()
+// would have copied it) instead of through a contiguous copy.  Null when TMA cannot address it.
+std::shared_ptr<Operator> gemm_with_operand_view(const Operator &op, int idx, const TensorDesc &view, bool tc_enabled) {
+    const GemmOp *g = as_gemm(op);
+    if (!g || idx < 0 || idx > 1 || view.dtype != SAGE_F32 || !gemm_runs_on_tc(op, tc_enabled)) return nullptr;
+    auto c = lowered_clone(*g);
+    const Shape &old = c->in[idx].shape, &sh = view.shape;
+    const int r = sh.rank(), ro = old.rank();
+    if (r < 2 || sh.extents[r - 2] != old.extents[ro - 2] || sh.extents[r - 1] != old.extents[ro - 1]) return nullptr;
+    long long b = 1;
+    for (int i = 0; i < r - 2; ++i) b *= sh.extents[i];
+    if (b != c->batch || !gemm_operand_view_ok(sh)) return nullptr;
+    c->in[idx] = view;
+    return c;
+}
+
+// Axis groups of `ext` (contiguous in the product's [batch, M, N] order).  False when an axis
+// straddles the row / column / batch boundaries.
+static bool classify_axes(const Array &ext, const Array &gstride, long long m, long long n, long long batch, std::vector<int> *group) {
+    group->assign(ext.size(), GCol);
+    long long total = 1;
+    int innermost_batch = -1;
+    long long innermost_batch_stride = 0;
+    for (size_t d = 0; d < ext.size(); ++d) {
+        total *= ext[d];
+        if (ext[d] == 1) continue;
+        const long long s = gstride[d];
+        if (s >= m * n) {
+            if (s % (m * n)) return false;
+            (*group)[d] = GBatchHi;
+            if (innermost_batch < 0 || s < innermost_batch_stride) {
+                innermost_batch = (int)d;
+                innermost_batch_stride = s;
+            }
+        } else if (s >= n) {
+            if (s % n || s * ext[d] > m * n) return false;
+            (*group)[d] = GRow;
+        } else {
+            if (s < 1 || s * ext[d] > n) return false;
+            (*group)[d] = GCol;
+        }
+    }
+    if (innermost_batch >= 0) (*group)[innermost_batch] = GBatchLo;
+    return total == batch * m * n;
+}
+
+// The map `expr` over (product, aux...) becomes the epilogue.  `aux` are the map's other operands
+// with the strides they will have at run time; `out` is the map's output.
+std::shared_ptr<Operator> gemm_with_epilogue(const Operator &op, const std::string &expr, const std::vector<TensorDesc> &aux,
+                                             const TensorDesc &out) {
+    const GemmOp *g = as_gemm(op);
+    if (!g || aux.size() > 3 || out.dtype != SAGE_F32) return nullptr;
+    auto c = lowered_clone(*g);
+    const Array &ext = out.shape.extents;
+    if (!classify_axes(ext, Shape::default_strides(ext), c->m, c->n, c->batch, &c->epi_group)) return nullptr;
+    for (const TensorDesc &a : aux)
+        if (a.dtype != SAGE_F32 || a.shape.extents != ext || !GemmOp::epilogue_operand_ok(a.shape, ext, c->epi_group)) return nullptr;
+    c->epi_ext = ext;
+    c->epilogue = expr;
+    c->in.resize(2);
+    for (const TensorDesc &a : aux) c->in.push_back(a);
+    c->out = out.pristine();
+    return c;
+}
+
+// A contiguous copy of `view` (a permuted / reshaped view of the product: extents + strides into
+// the product's row-major [batch, M, N] result) becomes the store pattern.
+std::shared_ptr<Operator> gemm_with_store(const Operator &op, const Shape &view, const TensorDesc &out, bool tc_enabled) {
+    const GemmOp *g = as_gemm(op);
+    if (!g || g->folded || view.offset != 0 || !gemm_runs_on_tc(op, tc_enabled)) return nullptr;
+    auto c = lowered_clone(*g);
+    const Array &ext = view.extents;
+    const Array dst = Shape::default_strides(ext);
+    std::vector<int> group;
+    if (!classify_axes(ext, view.strides, c->m, c->n, c->batch, &group)) return nullptr;
+    // per group, walking the axes from the smallest product-stride up: both the product strides and
+    // the destination strides must chain like one axis
+    std::vector<int> order;
+    for (size_t d = 0; d < ext.size(); ++d)
+        if (ext[d] > 1) order.push_back((int)d);
+    std::sort(order.begin(), order.end(), [&](int a, int b) { return view.strides[a] < view.strides[b]; });
+    long long expect_src = 1;
+    long long gdst[4] = {0, 0, 0, 0}, gspan[4] = {1, 1, 1, 1};
+    bool seen[4] = {false, false, false, false};
+    for (int d : order) {
+        if (view.strides[d] != expect_src) return nullptr;  // the view must enumerate the product exactly once
+        expect_src *= ext[d];
+        const int grp = group[d];
+        if (!seen[grp]) {
+            seen[grp] = true;
+            gdst[grp] = dst[d];
+        } else if (dst[d] != gdst[grp] * gspan[grp]) {
+            return nullptr;
+        }
+        gspan[grp] *= ext[d];
+    }
+    if (seen[GCol] && gdst[GCol] != 1) return nullptr;
+    if (gspan[GCol] != c->n || gspan[GRow] != c->m) return nullptr;
+    if (!c->epilogue.empty()) {  // the epilogue operands and the store must cut the batch the same way
+        long long e_nb0 = 1;
+        for (size_t d = 0; d < c->epi_ext.size(); ++d)
+            if (c->epi_group[d] == GBatchLo) e_nb0 *= c->epi_ext[d];
+        if (c->batch > 1 && e_nb0 != gspan[GBatchLo]) return nullptr;
+    }
+    c->folded = true;
+    c->ldc = gdst[GRow];
+    c->sc0 = gdst[GBatchLo];
+    c->sc1 = gdst[GBatchHi];
+    c->nbc0 = gspan[GBatchLo];
+    c->out = out.pristine();
+    return c;
+}
+
+bool is_gemm_op(const Operator &op) { return as_gemm(op) != nullptr; }
+
+std::string describe_gemm(const Operator &op) {
+    const GemmOp *g = as_gemm(op);
+    if (!g) return "";
+    std::string s;
+    if (!g->epilogue.empty()) s += "{" + g->epilogue + "}";
+    if (g->folded) s += "[store]";
+    return s;
+}
+
+// ------------------------------------------------------------------------------ constructors
 static void gemm_dims(const Array &e1, const Array &e2, size_t o, bool t1, bool t2, long long *h, long long *w) {
     const long long c1 = t1 ? e1[o] : e1[o + 1], c2 = t2 ? e2[o + 1] : e2[o];
     *h = t1 ? e1[o + 1] : e1[o];

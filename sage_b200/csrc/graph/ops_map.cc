@@ -79,6 +79,23 @@ const MapExpr *map_expr_of(const Operator &op) {
     return m ? &m->expr : nullptr;
 }
 
+bool is_copy_map(const Operator &op) {  // organize(): y = x
+    const MapOp *m = dynamic_cast<const MapOp *>(&op);
+    return m && m->in.size() == 1 && m->expr.kind == MapExpr::Un && m->expr.op == Copy && m->expr.args[0].kind == MapExpr::Input &&
+           m->out.dtype == m->in[0].dtype;
+}
+
+// The expression text with operand i renamed to x<remap[i]>.
+std::string map_expr_text_remap(const MapExpr &e, const std::vector<int> &remap) {
+    std::function<MapExpr(const MapExpr &)> walk = [&](const MapExpr &x) {
+        MapExpr r = x;
+        if (r.kind == MapExpr::Input) r.input = remap[r.input];
+        for (auto &a : r.args) a = walk(a);
+        return r;
+    };
+    return map_expr_text(walk(e));
+}
+
 static MapExpr input_expr(int i) {
     MapExpr e;
     e.kind = MapExpr::Input;
@@ -155,6 +172,32 @@ Var ops::cond(const Var &c0, const Var &x1, const Var &x2) {  // map.rs:861-883,
     op->expr.kind = MapExpr::Tern;
     op->expr.args = {input_expr(0), input_expr(1), input_expr(2)};
     return Var::from_op(op, {c, a, b});
+}
+
+// relu(x) = float(x > 0) * x (nn.rs:33-40) as ONE single-input map: the same expression, so the same
+// bits for every input (NaN, -inf and -0 included), but its operand is read once and the value
+// below it need not be materialised for having two readers.
+std::shared_ptr<Operator> make_relu_map(const TensorDesc &x) {
+    auto op = std::make_shared<MapOp>();
+    op->primitive = false;
+    op->in = {x};
+    op->out = x.pristine();
+    MapExpr zero;
+    zero.kind = MapExpr::Literal;
+    zero.bits = 0;
+    zero.lit_dtype = SAGE_F32;
+    MapExpr gt;
+    gt.kind = MapExpr::Bin;
+    gt.op = Gt;
+    gt.args = {input_expr(0), zero};
+    MapExpr cast;
+    cast.kind = MapExpr::Un;
+    cast.op = CastFloat;
+    cast.args = {gt};
+    op->expr.kind = MapExpr::Bin;
+    op->expr.op = Mul;
+    op->expr.args = {cast, input_expr(0)};
+    return op;
 }
 
 // ---------------------------------------------------------------- grads

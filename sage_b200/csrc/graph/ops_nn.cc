@@ -8,6 +8,8 @@
 namespace sage {
 using namespace ops;
 
+sage_status storage_planes_attach(Context &ctx, Storage &st);  // ops_gemm.cc
+
 enum RowKind { RSoftmax, RLse, RLayerNorm };
 
 struct RowOp : Operator {
@@ -24,20 +26,35 @@ struct RowOp : Operator {
     sage_status compute(const std::vector<Tensor> &x, Context &ctx, Tensor *y) override {
         if (!x[0].desc.shape.has_default_strides())
             return ctx.fail(SAGE_ERR_INVALID, std::string(name()) + ": input is not contiguous");
+        const bool emit = ctx.hint_emit_planes && kind != RLse;
+        ctx.hint_emit_planes = false;
         sage_status st = Tensor::uninit(ctx, out, y);
         if (st) return st;
         const float *xp = (const float *)x[0].ptr();
         float *yp = (float *)y->ptr();
+        float *hi = nullptr;
+        long long plane = 0;
+        if (emit) {  // a tensor-core GEMM reads y next: write its tf32 planes in the same pass
+            st = storage_planes_attach(ctx, *y->data);
+            if (st) return st;
+            hi = y->data->split->planes.planes + y->desc.shape.offset;
+            plane = y->data->split->plane;
+        }
         switch (kind) {
-        case RSoftmax: return k::softmax_rows(ctx, xp, yp, rows, cols);
+        case RSoftmax: return k::softmax_rows(ctx, xp, yp, rows, cols, hi, plane);
         case RLse: return k::lse_rows(ctx, xp, yp, rows, cols);
         case RLayerNorm:
             return k::layernorm_rows(ctx, xp, yp, rows, cols, (const float *)x[1].ptr(), x[1].desc.shape.size() == 1 ? 0 : 1,
-                                     (const float *)x[2].ptr(), x[2].desc.shape.size() == 1 ? 0 : 1, eps);
+                                     (const float *)x[2].ptr(), x[2].desc.shape.size() == 1 ? 0 : 1, eps, hi, plane);
         }
         return SAGE_ERR_INVALID;
     }
 };
+
+bool row_op_emits_planes(const Operator &op) {
+    const RowOp *r = dynamic_cast<const RowOp *>(&op);
+    return r && r->kind != RLse;
+}
 
 // True when `axes` are exactly the last axes of x and x is float + contiguous; fills rows/cols.
 static bool trailing(const Var &x, const std::vector<int> &axes, long long *rows, long long *cols) {
@@ -64,8 +81,12 @@ static void tag(const Var &y, RowKind kind, const std::vector<Var> &inputs, long
     y.origin->composite.reset(new Composite{op, inputs});
 }
 
+std::shared_ptr<Operator> make_relu_map(const TensorDesc &x);  // ops_map.cc
+
 Var ops::relu(const Var &x) {  // nn.rs:33-40
-    return mul(unary_map(binary_map(x, scalar_f(0.0f, {1}), Gt), CastFloat), x);
+    Var out = mul(unary_map(binary_map(x, scalar_f(0.0f, {1}), Gt), CastFloat), x);
+    if (x.dtype() == SAGE_F32) out.origin->composite.reset(new Composite{make_relu_map(x.desc), {x}});
+    return out;
 }
 
 Var ops::softmax(const Var &x, const std::vector<long long> &axes_in) {  // nn.rs:42-56

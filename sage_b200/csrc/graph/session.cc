@@ -21,7 +21,23 @@ struct Node {
     Var var;                       // data leaf: an input of the routine
     std::shared_ptr<Operator> op;  // operation
     std::vector<Node> args;
+    bool emit_planes = false;      // a tensor-core GEMM reads the result: ask the operator for its tf32 planes
 };
+
+// ops_map.cc / ops_core.cc / ops_gemm.cc / ops_nn.cc
+bool is_copy_map(const Operator &op);
+std::string map_expr_text_remap(const MapExpr &e, const std::vector<int> &remap);
+bool is_view_op(const Operator &op);
+bool is_reshape_op(const Operator &op);
+bool is_gemm_op(const Operator &op);
+bool gemm_runs_on_tc(const Operator &op, bool tc_enabled);
+bool gemm_can_fuse(const Operator &op, bool tc_enabled);
+std::shared_ptr<Operator> gemm_with_operand_view(const Operator &op, int idx, const TensorDesc &view, bool tc_enabled);
+std::shared_ptr<Operator> gemm_with_epilogue(const Operator &op, const std::string &expr, const std::vector<TensorDesc> &aux,
+                                             const TensorDesc &out);
+std::shared_ptr<Operator> gemm_with_store(const Operator &op, const Shape &view, const TensorDesc &out, bool tc_enabled);
+bool row_op_emits_planes(const Operator &op);
+std::string describe_gemm(const Operator &op);  // "{epilogue}" / "[store]" of a lowered GEMM, else empty
 
 struct Routine {
     std::vector<Var> inputs;
@@ -95,8 +111,101 @@ static Node build(const Var &v, const std::unordered_set<Origin *> &inputs, bool
     return n;
 }
 
+// ------------------------------------------------------------------------------ GEMM lowering
+// After a routine's tree is built, the operators around each tensor-core GEMM are folded into it
+// (no counterpart in the reference, whose GEMM is a library call between generated kernels):
+//   gemm(.. reshape(copy(view)) ..)        the operand is read through `view`; the copy goes away
+//   map(.. reshape(gemm) .., aux ..)       the map's expression becomes the GEMM's epilogue
+//   copy(permute(reshape(gemm)))           the permutation becomes the GEMM's store pattern
+// Every fold is checked against the static strides and declined when TMA or the epilogue's
+// addressing cannot express it; what is declined simply stays a separate kernel.
+static bool reshape_keeps_matrix(const Operator &op) {
+    const Array &a = op.in[0].shape.extents, &b = op.out.shape.extents;
+    const size_t ra = a.size(), rb = b.size();
+    return ra >= 2 && rb >= 2 && a[ra - 1] == b[rb - 1] && a[ra - 2] == b[rb - 2];
+}
+
+static void lower(Node &n, bool tc) {
+    if (n.is_data) return;
+    for (Node &a : n.args) lower(a, tc);
+    // operands behind an organize() copy
+    if (is_gemm_op(*n.op) && gemm_runs_on_tc(*n.op, tc)) {
+        for (int idx = 0; idx < 2; ++idx) {
+            Node *p = &n.args[idx];
+            while (!p->is_data && is_reshape_op(*p->op) && reshape_keeps_matrix(*p->op)) p = &p->args[0];
+            if (p->is_data || !is_copy_map(*p->op) || p->args.size() != 1) continue;
+            std::shared_ptr<Operator> f = gemm_with_operand_view(*n.op, idx, p->op->in[0], tc);
+            if (!f) continue;
+            Node inner = std::move(p->args[0]);
+            n.args[idx] = std::move(inner);
+            n.op = f;
+        }
+        return;
+    }
+    const MapExpr *expr = map_expr_of(*n.op);
+    if (!expr) return;
+    if (is_copy_map(*n.op)) {  // a permuted copy of a product
+        Node *p = &n.args[0];
+        while (!p->is_data && is_view_op(*p->op)) p = &p->args[0];
+        if (p != &n.args[0] && !p->is_data && is_gemm_op(*p->op)) {
+            std::shared_ptr<Operator> f = gemm_with_store(*p->op, n.op->in[0].shape, n.op->out, tc);
+            if (f) {
+                std::vector<Node> args = std::move(p->args);
+                n.op = f;
+                n.args = std::move(args);
+            }
+        }
+        return;
+    }
+    if (n.op->out.dtype != SAGE_F32) return;
+    for (size_t j = 0; j < n.args.size(); ++j) {  // a map over a product
+        Node *p = &n.args[j];
+        while (!p->is_data && is_reshape_op(*p->op)) p = &p->args[0];
+        if (p->is_data || !gemm_can_fuse(*p->op, tc) || p->op->out.shape.size() != n.op->out.shape.size()) continue;
+        std::vector<int> remap(n.args.size());
+        std::vector<TensorDesc> aux;
+        int next = 1;
+        for (size_t i = 0; i < n.args.size(); ++i) {
+            remap[i] = i == j ? 0 : next++;
+            if (i != j) aux.push_back(n.op->in[i]);
+        }
+        std::shared_ptr<Operator> f = gemm_with_epilogue(*p->op, map_expr_text_remap(*expr, remap), aux, n.op->out);
+        if (!f) continue;
+        std::vector<Node> args;
+        args.push_back(std::move(p->args[0]));
+        args.push_back(std::move(p->args[1]));
+        for (size_t i = 0; i < n.args.size(); ++i)
+            if (i != j) args.push_back(std::move(n.args[i]));
+        n.op = f;
+        n.args = std::move(args);
+        return;
+    }
+}
+
+// Which values a tensor-core GEMM reads (through views only): in-tree producers get emit_planes,
+// states are collected so that their routine's root gets it.
+static Node *skip_views(Node *p) {
+    while (!p->is_data && is_view_op(*p->op)) p = &p->args[0];
+    return p;
+}
+static bool can_emit_planes(const Operator &op, bool tc) { return gemm_runs_on_tc(op, tc) || row_op_emits_planes(op); }
+
+static void mark_plane_readers(Node &n, bool tc, std::unordered_set<Origin *> *states) {
+    if (n.is_data) return;
+    for (Node &a : n.args) mark_plane_readers(a, tc, states);
+    if (!is_gemm_op(*n.op) || !gemm_runs_on_tc(*n.op, tc)) return;
+    for (int idx = 0; idx < 2; ++idx) {
+        Node *p = skip_views(&n.args[idx]);
+        if (p->is_data) {
+            if (p->var.is_op()) states->insert(p->var.key());
+        } else if (can_emit_planes(*p->op, tc)) {
+            p->emit_planes = true;
+        }
+    }
+}
+
 // Program::compile, session.rs:62-206.
-static std::unique_ptr<Program> compile(const std::vector<Var> &x, std::vector<Var> y, bool fusion, bool pattern) {
+static std::unique_ptr<Program> compile(const std::vector<Var> &x, std::vector<Var> y, bool fusion, bool pattern, bool tc) {
     std::unique_ptr<Program> p(new Program());
     p->fusion = fusion;
     p->pattern = pattern;
@@ -175,7 +284,18 @@ static std::unique_ptr<Program> compile(const std::vector<Var> &x, std::vector<V
             if (v.is_op()) ++p->consumers[v.key()];
         }
         r.root = build(node, in_keys, fusion, pattern, true);
+        if (pattern) lower(r.root, tc);
         p->routines.emplace(node.key(), std::move(r));
+    }
+    if (pattern) {
+        std::unordered_set<Origin *> plane_states;
+        for (auto &kv : p->routines) mark_plane_readers(kv.second.root, tc, &plane_states);
+        for (Origin *key : plane_states) {
+            auto it = p->routines.find(key);
+            if (it == p->routines.end()) continue;  // an input of the program: split on first use
+            Node *root = skip_views(&it->second.root);
+            if (!root->is_data && can_emit_planes(*root->op, tc)) root->emit_planes = true;
+        }
     }
     p->outputs = y;
     return p;
@@ -211,7 +331,10 @@ static sage_status run_node(const Node &n, Context &ctx, Session &s, const std::
     for (size_t i = 0; i < args.size(); ++i)  // Operator::compute's spec check, ops.rs:163-178
         if (args[i].desc.shape.extents != n.op->in[i].shape.extents)
             return ctx.fail(SAGE_ERR_INVALID, std::string("operand extents differ from the operator's spec in ") + n.op->name());
-    return n.op->compute(args, ctx, out);
+    ctx.hint_emit_planes = n.emit_planes;
+    sage_status st = n.op->compute(args, ctx, out);
+    ctx.hint_emit_planes = false;
+    return st;
 }
 
 // Program::exec, session.rs:208-468.
@@ -317,7 +440,7 @@ sage_status Session::eval(const std::vector<Var> &targets) {
     if (!prog) {
         std::unique_ptr<Program> p;
         try {
-            p = compile(x, y, true, ctx_->opts().pattern_fusion != 0);
+            p = compile(x, y, true, ctx_->opts().pattern_fusion != 0, ctx_->opts().gemm_backend != 1);
         } catch (const ShapeError &e) {
             return ctx_->fail(SAGE_ERR_INVALID, e.msg);
         }
@@ -342,6 +465,8 @@ static void describe_node(const Node &n, std::string *out) {
     }
     out->append(n.op->name());
     if (const MapExpr *e = map_expr_of(*n.op)) out->append("{" + map_expr_text(*e) + "}");
+    out->append(describe_gemm(*n.op));
+    if (n.emit_planes) out->append("+planes");
     out->push_back('(');
     for (size_t i = 0; i < n.args.size(); ++i) {
         if (i) out->push_back(',');

@@ -27,10 +27,12 @@ sage_status reduce_arg(Context &ctx, bool is_max, const float *x, const Dims &ou
                        long long inner_str, uint32_t *y);
 
 // rowops.cu — softmax / log_sum_exp / layer_norm over contiguous rows (src/ops/nn.rs:42-100)
-sage_status softmax_rows(Context &ctx, const float *x, float *y, long long rows, long long cols);
+// `hi` (optional): also write the tf32 hi / lo planes of y, laid out like y, lo `plane` floats after hi.
+sage_status softmax_rows(Context &ctx, const float *x, float *y, long long rows, long long cols, float *hi = nullptr,
+                         long long plane = 0);
 sage_status lse_rows(Context &ctx, const float *x, float *y, long long rows, long long cols);
 sage_status layernorm_rows(Context &ctx, const float *x, float *y, long long rows, long long cols, const float *gamma,
-                           int gamma_stride, const float *beta, int beta_stride, float eps);
+                           int gamma_stride, const float *beta, int beta_stride, float eps, float *hi = nullptr, long long plane = 0);
 
 // index.cu — gather / scatter / strided copy (src/ops/core.rs:571-934)
 sage_status gather(Context &ctx, const uint32_t *x, const long long *x_str, const uint32_t *ind, const Dims &ind_dims,
@@ -80,6 +82,48 @@ sage_status split_tf32_into(Context &ctx, const float *src, long long ld, long l
                             float *dst, SplitPlanes *out);
 // `a` / `b` are the splits of g.a / g.b (as stored); g.a / g.b themselves are not read.
 sage_status gemm_tcgen05_planes(Context &ctx, const GemmArgs &g, const SplitPlanes &a, const SplitPlanes &b);
+
+// ---- the general form of the tensor-core GEMM, used by the evaluator's fused GEMM operator.
+// A split operand as the tensor core reads it: `rows` x `cols` with cols contiguous, rows `ld` floats
+// apart, batch index = b1 * nb0 + b0 at b0 * sb0 + b1 * sb1 floats.  `hi` points at the first
+// element of the tf32 high parts; the low parts lie `plane` floats further.  hi must be 16-byte
+// aligned and ld, sb0, sb1, plane multiples of 4 (TMA strides are multiples of 16 bytes).
+struct TcOperand {
+    const float *hi = nullptr;
+    long long plane = 0, ld = 0;
+    long long rows = 0, cols = 0;
+    long long nb0 = 1, nb1 = 1, sb0 = 0, sb1 = 0;
+};
+bool tc_operand_ok(const TcOperand &o);
+// An extra operand of the epilogue expression: element (batch, row, col) of the output reads
+// ptr[b0 * s0 + b1 * s1 + row * sr + col * sc] with the output's batch decomposition; sc is 0 or 1.
+struct TcAuxArg {
+    const float *ptr = nullptr;
+    long long s0 = 0, s1 = 0, sr = 0;
+    int sc = 0;
+};
+struct TcGemm {
+    bool a_kmajor = true, b_kmajor = false;  // is K the contiguous axis of the operand as stored
+    long long m = 0, n = 0, k = 0, batch = 1;
+    TcOperand a, b;
+    float *c = nullptr;      // fp32 result (may be null when only planes are wanted)
+    float *c_hi = nullptr;   // hi plane of the result, laid out like c (may be null)
+    long long c_plane = 0;   // floats from the hi to the lo plane
+    long long ldc = 0, sc0 = 0, sc1 = 0, nbc0 = 1;  // result (batch, row, col) at b0 * sc0 + b1 * sc1 + row * ldc + col
+    int naux = 0;
+    TcAuxArg aux[3];
+    std::string epilogue;    // C expression over x0 (the product) and x1..x3 (aux); empty = x0
+};
+bool gemm_tc_shape_ok(long long m, long long n, long long k, long long batch);
+sage_status gemm_tc_run(Context &ctx, const TcGemm &g);
+// hi/lo split of `n` consecutive floats into planes laid out like the source (dst_hi[i], dst_hi[plane + i]).
+sage_status split_tf32_flat(Context &ctx, const float *src, long long n, float *dst_hi, long long plane);
+// hi/lo split of a strided 4-level view (b1, b0, row, col) into compact planes owned by `out`.
+struct SplitView {
+    long long nb1 = 1, nb0 = 1, rows = 0, cols = 0;
+    long long sb1 = 0, sb0 = 0, ld = 0, col_stride = 1;
+};
+sage_status split_tf32_view(Context &ctx, const float *src, const SplitView &v, SplitPlanes *out);
 sage_status gemm_simt(Context &ctx, const GemmArgs &g);
 // Returns SAGE_ERR_UNSUPPORTED when the shape/alignment cannot go through TMA; the caller
 // then uses gemm_simt.

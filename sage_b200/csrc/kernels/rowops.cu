@@ -12,9 +12,11 @@
 // A warp owns a row when it fits in registers (cols <= 2048, cols % 4 == 0): lanes read float4
 // chunks `lane + 32*i`, so each pass over HBM is one coalesced read and one coalesced write.
 // Other shapes use a CTA per row that re-reads the row (L2-resident) per pass.
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include "kernels.h"
+#include "gemm_tc_device.inc"  // split_tf32_value
 
 namespace sage {
 namespace k {
@@ -40,7 +42,31 @@ struct RowParams {
     int gamma_stride, beta_stride;
     float eps;
     int ref_compat;
+    float *hi;        // when set: also write the tf32 hi / lo planes of y (softmax, layer_norm), laid out like y
+    long long plane;  // floats from the hi to the lo plane
 };
+
+__device__ __forceinline__ void row_store4(const RowParams &p, long long at, float4 o) {
+    *reinterpret_cast<float4 *>(p.y + at) = o;
+    if (p.hi) {
+        float4 h, l;
+        sage_tc::split_tf32_value(o.x, &h.x, &l.x);
+        sage_tc::split_tf32_value(o.y, &h.y, &l.y);
+        sage_tc::split_tf32_value(o.z, &h.z, &l.z);
+        sage_tc::split_tf32_value(o.w, &h.w, &l.w);
+        *reinterpret_cast<float4 *>(p.hi + at) = h;
+        *reinterpret_cast<float4 *>(p.hi + p.plane + at) = l;
+    }
+}
+__device__ __forceinline__ void row_store1(const RowParams &p, long long at, float o) {
+    p.y[at] = o;
+    if (p.hi) {
+        float h, l;
+        sage_tc::split_tf32_value(o, &h, &l);
+        p.hi[at] = h;
+        p.hi[p.plane + at] = l;
+    }
+}
 
 // V = float4 chunks per lane; the row has cols/4 <= 32*V chunks.
 template <int MODE, int V>
@@ -81,7 +107,7 @@ __global__ void __launch_bounds__(256) row_warp_kernel(RowParams p) {
                 o.y = (v[i].y - mean) / denom * p.gamma[(e + 1) * p.gamma_stride] + p.beta[(e + 1) * p.beta_stride];
                 o.z = (v[i].z - mean) / denom * p.gamma[(e + 2) * p.gamma_stride] + p.beta[(e + 2) * p.beta_stride];
                 o.w = (v[i].w - mean) / denom * p.gamma[(e + 3) * p.gamma_stride] + p.beta[(e + 3) * p.beta_stride];
-                yr[c] = o;
+                row_store4(p, row * p.cols + 4LL * c, o);
             }
         }
         return;
@@ -117,7 +143,7 @@ __global__ void __launch_bounds__(256) row_warp_kernel(RowParams p) {
             o.y = v[i].y / s;
             o.z = v[i].z / s;
             o.w = v[i].w / s;
-            yr[c] = o;
+            row_store4(p, row * p.cols + 4LL * c, o);
         }
     }
 }
@@ -173,7 +199,7 @@ __global__ void __launch_bounds__(256) row_cta_kernel(RowParams p) {
                 o.y = (v[i].y - mean) / denom * p.gamma[(e + 1) * p.gamma_stride] + p.beta[(e + 1) * p.beta_stride];
                 o.z = (v[i].z - mean) / denom * p.gamma[(e + 2) * p.gamma_stride] + p.beta[(e + 2) * p.beta_stride];
                 o.w = (v[i].w - mean) / denom * p.gamma[(e + 3) * p.gamma_stride] + p.beta[(e + 3) * p.beta_stride];
-                yr[c] = o;
+                row_store4(p, row * p.cols + 4LL * c, o);
             }
         }
         return;
@@ -203,7 +229,7 @@ __global__ void __launch_bounds__(256) row_cta_kernel(RowParams p) {
 #pragma unroll
     for (int i = 0; i < V; ++i) {
         const int c = threadIdx.x + 256 * i;
-        if (c < chunks) yr[c] = make_float4(v[i].x / s, v[i].y / s, v[i].z / s, v[i].w / s);
+        if (c < chunks) row_store4(p, row * p.cols + 4LL * c, make_float4(v[i].x / s, v[i].y / s, v[i].z / s, v[i].w / s));
     }
 }
 
@@ -228,7 +254,7 @@ __global__ void __launch_bounds__(256) row_block_kernel(RowParams p) {
         const float var = s2 / n - mean * mean;
         const float denom = sqrtf(var + p.eps);
         for (long long j = threadIdx.x; j < p.cols; j += blockDim.x)
-            yr[j] = (xr[j] - mean) / denom * p.gamma[j * p.gamma_stride] + p.beta[j * p.beta_stride];
+            row_store1(p, row * p.cols + j, (xr[j] - mean) / denom * p.gamma[j * p.gamma_stride] + p.beta[j * p.beta_stride]);
         return;
     }
     float m = -INFINITY;
@@ -242,7 +268,7 @@ __global__ void __launch_bounds__(256) row_block_kernel(RowParams p) {
         if (threadIdx.x == 0) p.y[row] = logf(s) + m;
         return;
     }
-    for (long long j = threadIdx.x; j < p.cols; j += blockDim.x) yr[j] = expf(xr[j] - m) / s;
+    for (long long j = threadIdx.x; j < p.cols; j += blockDim.x) row_store1(p, row * p.cols + j, expf(xr[j] - m) / s);
 }
 
 template <int MODE>
@@ -251,7 +277,8 @@ static sage_status launch_rows(Context &ctx, RowParams p, const char *name) {
     if (ctx.dry() || p.rows == 0) return SAGE_OK;
     p.ref_compat = ctx.opts().ref_compat;
     const bool aligned = (reinterpret_cast<uintptr_t>(p.x) % 16 == 0) &&
-                         (MODE == ROW_LSE || reinterpret_cast<uintptr_t>(p.y) % 16 == 0);
+                         (MODE == ROW_LSE || reinterpret_cast<uintptr_t>(p.y) % 16 == 0) &&
+                         (!p.hi || (reinterpret_cast<uintptr_t>(p.hi) % 16 == 0 && p.plane % 4 == 0));
     if (p.cols % 4 == 0 && p.cols <= 2048 && aligned) {
         const int chunks = (int)(p.cols / 4);
         const int v = (chunks + 31) / 32;
@@ -275,19 +302,19 @@ static sage_status launch_rows(Context &ctx, RowParams p, const char *name) {
     return ctx.check_cuda(cudaGetLastError(), name);
 }
 
-sage_status softmax_rows(Context &ctx, const float *x, float *y, long long rows, long long cols) {
-    RowParams p{x, y, rows, cols, nullptr, nullptr, 0, 0, 0.f, 1};
+sage_status softmax_rows(Context &ctx, const float *x, float *y, long long rows, long long cols, float *hi, long long plane) {
+    RowParams p{x, y, rows, cols, nullptr, nullptr, 0, 0, 0.f, 1, hi, plane};
     return launch_rows<ROW_SOFTMAX>(ctx, p, "softmax_rows");
 }
 
 sage_status lse_rows(Context &ctx, const float *x, float *y, long long rows, long long cols) {
-    RowParams p{x, y, rows, cols, nullptr, nullptr, 0, 0, 0.f, 1};
+    RowParams p{x, y, rows, cols, nullptr, nullptr, 0, 0, 0.f, 1, nullptr, 0};
     return launch_rows<ROW_LSE>(ctx, p, "lse_rows");
 }
 
 sage_status layernorm_rows(Context &ctx, const float *x, float *y, long long rows, long long cols, const float *gamma,
-                           int gamma_stride, const float *beta, int beta_stride, float eps) {
-    RowParams p{x, y, rows, cols, gamma, beta, gamma_stride, beta_stride, eps, 1};
+                           int gamma_stride, const float *beta, int beta_stride, float eps, float *hi, long long plane) {
+    RowParams p{x, y, rows, cols, gamma, beta, gamma_stride, beta_stride, eps, 1, hi, plane};
     return launch_rows<ROW_LN>(ctx, p, "layernorm_rows");
 }
 

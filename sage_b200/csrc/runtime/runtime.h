@@ -142,6 +142,9 @@ public:
 
     void *timer_events[2] = {nullptr, nullptr};  // cudaEvent_t pair of sage_timer_start/stop
     uint32_t *status_word_dev = nullptr;  // device word kernels OR error bits into
+    // Set by the evaluator around one operator's compute(): a tensor-core GEMM will read the result,
+    // so a producer that can should also write the tf32 hi/lo planes of what it computes.
+    bool hint_emit_planes = false;
     int sm_count = 148;
 
 private:

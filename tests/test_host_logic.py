@@ -227,9 +227,38 @@ def test_bert_base_plan():
     c.eval(logits)
     # same program replayed; the tf32 splits of the 72 weight matrices are cached on their storages
     assert c.programs_compiled() == 1 and c.launch_count()[0] - k0 == len(t) - 72
-    # per layer 6 weights + 8 activations (the layer input is split once for Q, K and V)
-    assert t.count("split_tf32") == 12 * 14 and t.count("gemm_tc_3xtf32") == 96
+    # Only the weights go through a split pass: every activation a GEMM reads gets its tf32 planes
+    # from the kernel that produces it (GEMM epilogue, softmax, layer norm).
+    assert t.count("split_tf32") == 72 and t.count("gemm_tc_3xtf32") == 96
+    # bias / residual / relu / scale+mask maps and the head split / merge copies are folded into the
+    # GEMMs; what is left is the embedding sum, the per-layer mask bias and the classifier's two maps
+    assert t.count("sage_map") == 1 + 12 + 2
+    d = c.describe()
+    assert d.count("gemm_batched[store]+planes") == 12                       # head merge = store pattern of P.V
+    assert d.count("gemm_batched{((x0 / sg_lit(0x41000000u)) + x1)}") == 12  # scores: scale + mask in the epilogue
+    assert d.count("gemm{(((float)((x0 + x1) > sg_lit(0x00000000u))) * (x0 + x1))}+planes") == 12  # FFN up: bias + relu
+    assert d.count("gemm{((x0 + x1) + x2)}") == 24                           # output / FFN down: bias + residual
+    assert d.count("softmax+planes") == 12 and d.count("layer_norm+planes") == 24
     assert c.mem_stats()["mem_peak"] < 3 << 30
+    c.close()
+
+
+def test_bert_plan_without_pattern_fusion_is_the_reference_decomposition():
+    """pattern_fusion = 0: no composites, no GEMM lowering — every operator of the reference's graph is
+    its own kernel (the evaluator of src/session.rs with map fusion only)."""
+    c = S.Context(-1, pattern_fusion=0)
+    model = S.Bert(num_vocabs=64, embed_dim=64, num_heads=2, seq_len=64, ffn_dim=128, num_layers=1, num_classes=3)
+    for p in model.params():
+        c.set(p, np.zeros(p.extents, np.float32))
+    logits = model.pass_(c.var(np.zeros((4, 64), np.uint32)), c.var(np.ones((4, 64), np.float32)))
+    c.trace_begin()
+    c.eval(logits)
+    t = c.trace()
+    d = c.describe()
+    assert "layernorm_rows" not in t and "softmax_rows" not in t
+    assert "[store]" not in d and "+planes" not in d and "gemm{" not in d and "gemm_batched{" not in d
+    # every operand goes through a split pass (the layer input once for its three readers Q, K, V)
+    assert t.count("gemm_tc_3xtf32") == 8 and t.count("split_tf32") == 2 * 8 - 2
     c.close()
 
 
