@@ -6,6 +6,7 @@ row kernels and f32-equivalent TFLOP/s of the tensor-core GEMM, each as one JSON
   python -m sage_b200.microbench --case reduce|softmax|layernorm|lse --rows 16384 --cols 4096
   python -m sage_b200.microbench --case config1 --rows 16384 --cols 4096  # whole forward + grad graph
   python -m sage_b200.microbench --case all
+  python -m sage_b200.microbench --case tf32_peak                          # library TF32 GEMM: the tensor-pipe denominator
 
 Times are device times from CUDA events recorded on the context's stream in front of every launch
 (Context.profile_begin / profile_end).  Algorithmic bytes: every distinct input once + the output once.
@@ -105,6 +106,37 @@ def case_config1(ctx, a):
             "peak_hbm_gb_per_s": hbm, "frac": gbs / hbm, "peak_source": src, "kernels": {k: v for k, v in prof.items()}}
 
 
+def case_tf32_peak(a):
+    """The tensor-pipe denominator for 3xTF32: the library TF32 GEMM (torch.matmul with TF32 allowed) at
+    8192^3, measured like the bf16 figure of MEASURED_PEAKS.json — a burst of 10 and a loop of ~3 s."""
+    import time
+    import torch
+    torch.backends.cuda.matmul.allow_tf32 = True
+    dev = "cuda:%d" % a.device
+    n = 8192
+    x, y = torch.randn(n, n, device=dev), torch.randn(n, n, device=dev)
+    for _ in range(3):
+        x @ y
+    torch.cuda.synchronize()
+
+    def run(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            x @ y
+        e1.record()
+        torch.cuda.synchronize()
+        return 2.0 * n ** 3 * iters / (e0.elapsed_time(e1) * 1e-3) / 1e12
+    burst = max(run(10) for _ in range(3))
+    t0 = time.time()
+    sustained = []
+    while time.time() - t0 < 3.0:
+        sustained.append(run(50))
+    return {"case": "tf32_peak", "n": n, "tf32_tflops_burst": burst, "tf32_tflops_sustained": sustained[-1],
+            "f32_equivalent_ceiling_3xtf32_burst": burst / 3, "f32_equivalent_ceiling_3xtf32_sustained": sustained[-1] / 3,
+            "method": "torch.matmul fp32 inputs, allow_tf32=True (library kernel; used only as the roofline denominator)"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", default="all")
@@ -117,6 +149,9 @@ def main():
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--device", type=int, default=0)
     a = ap.parse_args()
+    if a.case == "tf32_peak":
+        print(json.dumps(case_tf32_peak(a)), flush=True)
+        return
     ctx = S.Context(a.device)
     cases = ["gemm", "map", "reduce", "softmax", "lse", "layernorm", "config1"] if a.case == "all" else [a.case]
     for c in cases:
