@@ -81,9 +81,11 @@ struct SplitCache {
 struct Storage {
     std::shared_ptr<SplitCache> split;       // whole-storage planes
     std::shared_ptr<SplitCache> split_view;  // last compact split of a view
+    uint64_t version = 0;                    // bumped whenever the contents are rewritten
     void drop_splits() {
         split.reset();
         split_view.reset();
+        ++version;
     }
     Context *ctx = nullptr;  // identity only; never dereferenced by the destructor
     std::shared_ptr<Allocator> alloc;

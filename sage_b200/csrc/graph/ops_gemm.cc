@@ -12,6 +12,8 @@
 //     the GEMM's epilogue expression;
 //   * a permuted copy of the product (head merge) becomes the GEMM's store pattern;
 //   * the product's tf32 hi/lo planes are written by the epilogue when another GEMM reads it next.
+#include <cuda_runtime.h>
+
 #include "graph.h"
 
 namespace sage {
@@ -472,6 +474,195 @@ std::string describe_gemm(const Operator &op) {
     if (!g->epilogue.empty()) s += "{" + g->epilogue + "}";
     if (g->folded) s += "[store]";
     return s;
+}
+
+// ------------------------------------------------------------------------------ grouped GEMM
+// Several GEMMs that read the same A (the query / key / value projections of one layer input) run as
+// ONE batched launch: batch g multiplies A by weight g and writes slab g of a [G, M, N] result.  A is
+// a broadcast operand; the G weights (and biases) are copied once into one allocation so that the
+// batch is a constant stride, and copied again only when a weight is rewritten (Storage::version).
+// No counterpart in the reference; the evaluator forms groups when it lowers a routine.
+struct GroupedGemmOp : Operator {
+    int groups = 0;
+    bool ta = false, tb = false, has_bias = false;
+    long long m = 0, n = 0, k = 0;
+    std::string epilogue;  // over x0 (product) and, with has_bias, x1 (the bias row)
+
+    struct Concat {
+        std::vector<std::pair<const Storage *, uint64_t>> key;
+        std::shared_ptr<Allocator> alloc;
+        Block *block = nullptr;
+        ~Concat() {
+            if (alloc && block) alloc->free(block);
+        }
+    };
+    std::unique_ptr<Concat> weights, biases;
+
+    const char *name() const override { return "gemm_grouped"; }
+    Cat cat() const override { return Cat::Contract; }
+    std::vector<Var> grad(const std::vector<Var> &, const Var &, const Var &) override {
+        shape_fail("a grouped gemm is not differentiated; grad walks the separate gemms");
+    }
+
+    static bool same_key(const Concat *c, const std::vector<Tensor> &x, int first, int count) {
+        if (!c || (int)c->key.size() != count) return false;
+        for (int i = 0; i < count; ++i)
+            if (c->key[i].first != x[first + i].data.get() || c->key[i].second != x[first + i].data->version) return false;
+        return true;
+    }
+
+    sage_status compute(const std::vector<Tensor> &x, Context &ctx, Tensor *y) override {
+        const bool emit = ctx.hint_emit_planes;
+        ctx.hint_emit_planes = false;
+        sage_status st = Tensor::uninit(ctx, out, y);
+        if (st) return st;
+        const long long wsize = k * n;
+        // ---- weights: [G] planes of K x N (or N x K), hi plane then lo plane
+        if (!same_key(weights.get(), x, 1, groups)) {
+            std::unique_ptr<Concat> c(new Concat());
+            c->alloc = ctx.allocator_ptr();
+            c->block = ctx.allocator().alloc((size_t)groups * wsize * 2 * sizeof(float));
+            if (!c->block) return ctx.fail(SAGE_ERR_OOM, "out of memory for the grouped gemm's weights");
+            float *hi = reinterpret_cast<float *>(c->block->ptr), *lo = hi + groups * wsize;
+            for (int i = 0; i < groups; ++i) {
+                const Tensor &w = x[1 + i];
+                if (!w.desc.shape.has_default_strides()) return ctx.fail(SAGE_ERR_INVALID, "internal: grouped gemm weight is not contiguous");
+                st = storage_planes(ctx, *w.data);
+                if (st) return st;
+                const SplitCache &sp = *w.data->split;
+                const float *src = sp.planes.planes + w.desc.shape.offset;
+                if (!ctx.dry()) {
+                    st = ctx.check_cuda(cudaMemcpyAsync(hi + i * wsize, src, wsize * 4, cudaMemcpyDeviceToDevice, ctx.stream()), "grouped gemm weights");
+                    if (st) return st;
+                    st = ctx.check_cuda(cudaMemcpyAsync(lo + i * wsize, src + sp.plane, wsize * 4, cudaMemcpyDeviceToDevice, ctx.stream()), "grouped gemm weights");
+                    if (st) return st;
+                }
+                c->key.push_back({w.data.get(), w.data->version});
+            }
+            weights = std::move(c);
+        }
+        if (has_bias && !same_key(biases.get(), x, 1 + groups, groups)) {
+            std::unique_ptr<Concat> c(new Concat());
+            c->alloc = ctx.allocator_ptr();
+            c->block = ctx.allocator().alloc((size_t)groups * n * sizeof(float));
+            if (!c->block) return ctx.fail(SAGE_ERR_OOM, "out of memory for the grouped gemm's biases");
+            for (int i = 0; i < groups; ++i) {
+                const Tensor &b = x[1 + groups + i];  // a broadcast view of a contiguous [N] vector
+                if (b.desc.shape.strides.back() != 1) return ctx.fail(SAGE_ERR_INVALID, "internal: grouped gemm bias is not a row vector");
+                if (!ctx.dry()) {
+                    st = ctx.check_cuda(cudaMemcpyAsync(reinterpret_cast<float *>(c->block->ptr) + i * n, b.ptr(), n * 4, cudaMemcpyDeviceToDevice, ctx.stream()),
+                                        "grouped gemm biases");
+                    if (st) return st;
+                }
+                c->key.push_back({b.data.get(), b.data->version});
+            }
+            biases = std::move(c);
+        }
+        k::TcGemm g;
+        g.m = m;
+        g.n = n;
+        g.k = k;
+        g.batch = groups;
+        std::shared_ptr<SplitCache> hold_a;
+        bool sw_a = false;
+        st = make_operand(ctx, x[0], &g.a, &sw_a, &hold_a);
+        if (st) return st;
+        if (g.a.nb0 * g.a.nb1 != 1) return ctx.fail(SAGE_ERR_INVALID, "internal: grouped gemm operand has a batch");
+        g.a.bcast = true;
+        g.a_kmajor = (!ta) != sw_a;
+        g.b_kmajor = tb;
+        g.b.hi = reinterpret_cast<const float *>(weights->block->ptr);
+        g.b.plane = groups * wsize;
+        g.b.rows = tb ? n : k;
+        g.b.cols = tb ? k : n;
+        g.b.ld = g.b.cols;
+        g.b.nb0 = groups;
+        g.b.sb0 = wsize;
+        g.c = (float *)y->ptr();
+        g.ldc = n;
+        g.sc0 = m * n;
+        g.nbc0 = groups;
+        if (emit) {
+            st = storage_planes_attach(ctx, *y->data);
+            if (st) return st;
+            g.c_hi = y->data->split->planes.planes + y->desc.shape.offset;
+            g.c_plane = y->data->split->plane;
+        }
+        g.epilogue = epilogue;
+        if (has_bias) {
+            g.naux = 1;
+            g.aux[0].ptr = reinterpret_cast<const float *>(biases->block->ptr);
+            g.aux[0].s0 = n;
+            g.aux[0].sc = 1;
+        }
+        return k::gemm_tc_run(ctx, g);
+    }
+};
+
+// Slab i of a grouped product, shaped like the member GEMM's own result.
+struct SlabOp : Operator {
+    int index = 0;
+    const char *name() const override { return "slab"; }
+    std::vector<Var> grad(const std::vector<Var> &, const Var &, const Var &) override { shape_fail("slab is not differentiated"); }
+    sage_status compute(const std::vector<Tensor> &x, Context &, Tensor *y) override {
+        Shape s(out.shape.extents);
+        s.offset = x[0].desc.shape.offset + (long long)index * out.shape.size();
+        *y = x[0].with_shape(s);
+        return SAGE_OK;
+    }
+};
+
+bool is_slab_op(const Operator &op) { return dynamic_cast<const SlabOp *>(&op) != nullptr; }
+bool is_grouped_gemm_op(const Operator &op) { return dynamic_cast<const GroupedGemmOp *>(&op) != nullptr; }
+
+// Can this lowered GEMM join a group?  Fills a key that is equal for GEMMs that may share a launch
+// (same A view, same shape and transposes, same epilogue text); the caller adds A's identity.
+bool gemm_group_key(const Operator &op, std::string *key) {
+    const GemmOp *g = as_gemm(op);
+    if (!g || !g->lowered || g->folded || g->batch != 1 || g->naux() > 1) return false;
+    if (g->n % 4 || g->k % 4 || !g->in[1].shape.has_default_strides() || g->in[1].shape.rank() != 2) return false;
+    if (g->naux() == 1) {  // the one epilogue operand must be a row vector broadcast over the rows
+        const Shape &b = g->in[2].shape;
+        for (int d = 0; d < b.rank(); ++d) {
+            const bool last = d == b.rank() - 1;
+            if (b.extents[d] > 1 && b.strides[d] != (last ? 1 : 0)) return false;
+        }
+        if (b.extents.back() != g->n) return false;
+    }
+    const Shape &a = g->in[0].shape;
+    std::string s = std::to_string(g->m) + "x" + std::to_string(g->n) + "x" + std::to_string(g->k) + (g->ta ? "T" : "N") + (g->tb ? "T" : "N") + "|" +
+                    g->epilogue + "|" + std::to_string(g->naux()) + "|";
+    for (int d = 0; d < a.rank(); ++d) s += std::to_string(a.extents[d]) + ":" + std::to_string(a.strides[d]) + ",";
+    s += "@" + std::to_string(a.offset);
+    *key = s;
+    return true;
+}
+
+std::shared_ptr<Operator> make_grouped_gemm(const std::vector<const Operator *> &members) {
+    const GemmOp *g0 = as_gemm(*members[0]);
+    auto op = std::make_shared<GroupedGemmOp>();
+    op->groups = (int)members.size();
+    op->ta = g0->ta;
+    op->tb = g0->tb;
+    op->has_bias = g0->naux() == 1;
+    op->m = g0->m;
+    op->n = g0->n;
+    op->k = g0->k;
+    op->epilogue = g0->epilogue;
+    op->in.push_back(g0->in[0]);
+    for (const Operator *m : members) op->in.push_back(m->in[1]);
+    if (op->has_bias)
+        for (const Operator *m : members) op->in.push_back(m->in[2]);
+    op->out = TensorDesc(Array{(long long)members.size(), g0->m, g0->n}, SAGE_F32);
+    return op;
+}
+
+std::shared_ptr<Operator> make_slab(const Operator &grouped, int index, const TensorDesc &member_out) {
+    auto op = std::make_shared<SlabOp>();
+    op->index = index;
+    op->in = {grouped.out};
+    op->out = member_out.pristine();
+    return op;
 }
 
 // ------------------------------------------------------------------------------ constructors

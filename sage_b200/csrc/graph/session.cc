@@ -22,6 +22,9 @@ struct Node {
     std::shared_ptr<Operator> op;  // operation
     std::vector<Node> args;
     bool emit_planes = false;      // a tensor-core GEMM reads the result: ask the operator for its tf32 planes
+    std::shared_ptr<Node> shared;  // a node several parents read (a grouped GEMM): evaluated once per routine run,
+                                   // and passed to `op` as its only operand
+    bool visited = false;          // traversal mark for shared nodes
 };
 
 // ops_map.cc / ops_core.cc / ops_gemm.cc / ops_nn.cc
@@ -37,6 +40,10 @@ std::shared_ptr<Operator> gemm_with_epilogue(const Operator &op, const std::stri
                                              const TensorDesc &out);
 std::shared_ptr<Operator> gemm_with_store(const Operator &op, const Shape &view, const TensorDesc &out, bool tc_enabled);
 bool row_op_emits_planes(const Operator &op);
+bool is_grouped_gemm_op(const Operator &op);
+bool gemm_group_key(const Operator &op, std::string *key);
+std::shared_ptr<Operator> make_grouped_gemm(const std::vector<const Operator *> &members);
+std::shared_ptr<Operator> make_slab(const Operator &grouped, int index, const TensorDesc &member_out);
 std::string describe_gemm(const Operator &op);  // "{epilogue}" / "[store]" of a lowered GEMM, else empty
 
 struct Routine {
@@ -185,16 +192,80 @@ static void lower(Node &n, bool tc) {
 // Which values a tensor-core GEMM reads (through views only): in-tree producers get emit_planes,
 // states are collected so that their routine's root gets it.
 static Node *skip_views(Node *p) {
-    while (!p->is_data && is_view_op(*p->op)) p = &p->args[0];
-    return p;
+    for (;;) {
+        if (p->is_data) return p;
+        if (p->shared) p = p->shared.get();  // a slab of a grouped product
+        else if (is_view_op(*p->op)) p = &p->args[0];
+        else return p;
+    }
 }
-static bool can_emit_planes(const Operator &op, bool tc) { return gemm_runs_on_tc(op, tc) || row_op_emits_planes(op); }
+static bool can_emit_planes(const Operator &op, bool tc) {
+    return gemm_runs_on_tc(op, tc) || row_op_emits_planes(op) || is_grouped_gemm_op(op);
+}
+
+// GEMMs of one routine that multiply the same A (same leaf, same view) by different weights, with
+// the same shape and epilogue, become one grouped launch; each member turns into a slab view of the
+// shared node.  Members must take their weight (and bias) straight from data leaves, because the
+// grouped operator keeps a concatenated copy of them.
+static void collect_gemms(Node &n, std::vector<Node *> *out) {
+    if (n.is_data) return;
+    for (Node &a : n.args) collect_gemms(a, out);
+    if (is_gemm_op(*n.op)) out->push_back(&n);
+}
+
+static void group_gemms(Node &root) {
+    std::vector<Node *> gemms;
+    collect_gemms(root, &gemms);
+    std::unordered_map<std::string, std::vector<Node *>> by_key;
+    std::vector<std::string> order;
+    for (Node *g : gemms) {
+        std::string key;
+        if (!gemm_group_key(*g->op, &key)) continue;
+        Node *a = skip_views(&g->args[0]);
+        if (!a->is_data) continue;
+        bool leaves = true;
+        for (size_t i = 1; i < g->args.size(); ++i) {
+            Node *w = skip_views(&g->args[i]);
+            if (!w->is_data || w->var.is_op()) leaves = false;
+        }
+        if (!leaves) continue;
+        char id[32];
+        snprintf(id, sizeof id, "#%p", (void *)a->var.key());
+        key += id;
+        if (!by_key.count(key)) order.push_back(key);
+        by_key[key].push_back(g);
+    }
+    for (const std::string &key : order) {
+        std::vector<Node *> &members = by_key[key];
+        if (members.size() < 2) continue;
+        std::vector<const Operator *> ops;
+        for (Node *m : members) ops.push_back(m->op.get());
+        auto shared = std::make_shared<Node>();
+        shared->op = make_grouped_gemm(ops);
+        shared->args.push_back(std::move(members[0]->args[0]));
+        for (Node *m : members) shared->args.push_back(std::move(m->args[1]));
+        if (members[0]->args.size() > 2)
+            for (Node *m : members) shared->args.push_back(std::move(m->args[2]));
+        for (size_t i = 0; i < members.size(); ++i) {
+            Node *m = members[i];
+            std::shared_ptr<Operator> slab = make_slab(*shared->op, (int)i, m->op->out);
+            m->op = slab;
+            m->args.clear();
+            m->shared = shared;
+        }
+    }
+}
 
 static void mark_plane_readers(Node &n, bool tc, std::unordered_set<Origin *> *states) {
     if (n.is_data) return;
+    if (n.shared && !n.shared->visited) {
+        n.shared->visited = true;
+        mark_plane_readers(*n.shared, tc, states);
+    }
     for (Node &a : n.args) mark_plane_readers(a, tc, states);
-    if (!is_gemm_op(*n.op) || !gemm_runs_on_tc(*n.op, tc)) return;
-    for (int idx = 0; idx < 2; ++idx) {
+    const bool grouped = is_grouped_gemm_op(*n.op);
+    if (!grouped && (!is_gemm_op(*n.op) || !gemm_runs_on_tc(*n.op, tc))) return;
+    for (int idx = 0; idx < (grouped ? 1 : 2); ++idx) {
         Node *p = skip_views(&n.args[idx]);
         if (p->is_data) {
             if (p->var.is_op()) states->insert(p->var.key());
@@ -284,7 +355,10 @@ static std::unique_ptr<Program> compile(const std::vector<Var> &x, std::vector<V
             if (v.is_op()) ++p->consumers[v.key()];
         }
         r.root = build(node, in_keys, fusion, pattern, true);
-        if (pattern) lower(r.root, tc);
+        if (pattern) {
+            lower(r.root, tc);
+            if (tc) group_gemms(r.root);
+        }
         p->routines.emplace(node.key(), std::move(r));
     }
     if (pattern) {
@@ -302,8 +376,10 @@ static std::unique_ptr<Program> compile(const std::vector<Var> &x, std::vector<V
 }
 
 // Routine::exec, session.rs:612-673 (a recursive walk instead of the flattened stack).
+typedef std::unordered_map<const Node *, Tensor> SharedMemo;  // results of shared nodes during one routine run
+
 static sage_status run_node(const Node &n, Context &ctx, Session &s, const std::unordered_map<Origin *, Tensor> &temp,
-                            Tensor *out) {
+                            SharedMemo &memo, Tensor *out) {
     if (n.is_data) {
         Origin *o = n.var.key();
         if (!n.var.is_op()) {
@@ -325,8 +401,18 @@ static sage_status run_node(const Node &n, Context &ctx, Session &s, const std::
     }
     std::vector<Tensor> args(n.args.size());
     for (size_t i = 0; i < n.args.size(); ++i) {
-        sage_status st = run_node(n.args[i], ctx, s, temp, &args[i]);
+        sage_status st = run_node(n.args[i], ctx, s, temp, memo, &args[i]);
         if (st) return st;
+    }
+    if (n.shared) {
+        auto it = memo.find(n.shared.get());
+        if (it == memo.end()) {
+            Tensor t;
+            sage_status st = run_node(*n.shared, ctx, s, temp, memo, &t);
+            if (st) return st;
+            it = memo.emplace(n.shared.get(), t).first;
+        }
+        args.insert(args.begin(), it->second);
     }
     for (size_t i = 0; i < args.size(); ++i)  // Operator::compute's spec check, ops.rs:163-178
         if (args[i].desc.shape.extents != n.op->in[i].shape.extents)
@@ -369,7 +455,8 @@ static sage_status exec(Program &p, Context &ctx, Session &s) {
         Tensor out;
         for (;;) {
             auto t0 = std::chrono::steady_clock::now();
-            sage_status st = run_node(f.root, ctx, s, temp, &out);
+            SharedMemo memo;
+            sage_status st = run_node(f.root, ctx, s, temp, memo, &out);
             f.exec_time = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
             if (st == SAGE_OK) break;
             if (st != SAGE_ERR_OOM) return st;
@@ -468,6 +555,7 @@ static void describe_node(const Node &n, std::string *out) {
     out->append(describe_gemm(*n.op));
     if (n.emit_planes) out->append("+planes");
     out->push_back('(');
+    if (n.shared) describe_node(*n.shared, out);
     for (size_t i = 0; i < n.args.size(); ++i) {
         if (i) out->push_back(',');
         describe_node(n.args[i], out);

@@ -93,6 +93,7 @@ struct TcOperand {
     long long plane = 0, ld = 0;
     long long rows = 0, cols = 0;
     long long nb0 = 1, nb1 = 1, sb0 = 0, sb1 = 0;
+    bool bcast = false;  // one matrix shared by every batch of the GEMM (nb0 = nb1 = 1)
 };
 bool tc_operand_ok(const TcOperand &o);
 // An extra operand of the epilogue expression: element (batch, row, col) of the output reads

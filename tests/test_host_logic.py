@@ -221,7 +221,7 @@ def test_bert_base_plan():
     t = c.trace()
     assert t.count("layernorm_rows") == 25 and t.count("softmax_rows") == 12
     gemms = [k for k in t if k.startswith("gemm")]
-    assert len(gemms) == 12 * 8 + 1
+    assert len(gemms) == 12 * 6 + 1  # per layer: grouped Q/K/V, scores, P.V, output, FFN up, FFN down; + classifier
     k0, _ = c.launch_count()
     c.clear()
     c.eval(logits)
@@ -229,11 +229,13 @@ def test_bert_base_plan():
     assert c.programs_compiled() == 1 and c.launch_count()[0] - k0 == len(t) - 72
     # Only the weights go through a split pass: every activation a GEMM reads gets its tf32 planes
     # from the kernel that produces it (GEMM epilogue, softmax, layer norm).
-    assert t.count("split_tf32") == 72 and t.count("gemm_tc_3xtf32") == 96
+    assert t.count("split_tf32") == 72 and t.count("gemm_tc_3xtf32") == 72
     # bias / residual / relu / scale+mask maps and the head split / merge copies are folded into the
     # GEMMs; what is left is the embedding sum, the per-layer mask bias and the classifier's two maps
     assert t.count("sage_map") == 1 + 12 + 2
     d = c.describe()
+    # the three projections of a layer input are one grouped launch, read back as three slabs
+    assert d.count("slab(gemm_grouped+planes(") == 36
     assert d.count("gemm_batched[store]+planes") == 12                       # head merge = store pattern of P.V
     assert d.count("gemm_batched{((x0 / sg_lit(0x41000000u)) + x1)}") == 12  # scores: scale + mask in the epilogue
     assert d.count("gemm{(((float)((x0 + x1) > sg_lit(0x00000000u))) * (x0 + x1))}+planes") == 12  # FFN up: bias + relu
