@@ -1,0 +1,180 @@
+"""The evaluator's GEMM lowering on the GPU: operand views instead of organize() copies, epilogue
+fusion, store patterns, grouped launches and producer-written tf32 planes must not change results.
+Every case is evaluated three ways — lowered (default), with pattern_fusion = 0 (the reference's
+decomposition, every operator its own kernel) and in float64 NumPy — and the lowered program is
+checked to really contain the folds it is meant to exercise.
+
+Tolerance: contractions are compared as |a - b| / max(|b|, rms(b)) <= 1e-4 against float64 (the
+bound stated for f32 results); lowered vs decomposed differ only by the order of a few fp32
+roundings in the epilogue (x*W + b evaluated in one kernel instead of two), so they agree to 1e-5.
+"""
+import numpy as np
+import pytest
+
+import sage_b200 as S
+
+pytestmark = pytest.mark.gpu
+
+
+def gemm_err(got, ref):
+    a, b = np.asarray(got, np.float64), np.asarray(ref, np.float64)
+    assert a.shape == b.shape, (a.shape, b.shape)
+    rms = max(float(np.sqrt((b ** 2).mean())), 1e-30)
+    return float((np.abs(a - b) / np.maximum(np.abs(b), rms)).max())
+
+
+def softmax64(x):
+    e = np.exp(x - x.max(-1, keepdims=True))
+    return e / e.sum(-1, keepdims=True)
+
+
+def attention_block(ctx, a, heads):
+    """One post-LN transformer block written with the public ops, as src/models/bert.rs does."""
+    n, l, e = a["x"].shape
+    d = e // heads
+    x = ctx.var(a["x"])
+    v = {k: ctx.var(a[k]) for k in a if k != "x"}
+
+    def split(t):
+        return S.view(t, (n, l, heads, d)).permute((0, 2, 1, 3))
+    q, k, val = (split(x.matmul(v["w" + s]) + v["b" + s]) for s in "qkv")
+    scores = q.matmul_batched(k.transpose(-1, -2)) / float(np.sqrt(d)) + v["mask"]
+    p = S.softmax(scores, [-1])
+    merged = S.view(p.matmul_batched(val).permute((0, 2, 1, 3)), (n, l, e))
+    o = merged.matmul(v["wo"]) + v["bo"] + x
+    h = S.relu(o.matmul(v["w1"]) + v["b1"])
+    out = h.matmul(v["w2"]) + v["b2"] + o
+    return dict(scores=scores, p=p, merged=merged, o=o, out=out), v
+
+
+def attention_block64(a, heads):
+    f = {k: np.asarray(t, np.float64) for k, t in a.items()}
+    n, l, e = f["x"].shape
+    d = e // heads
+
+    def split(t):
+        return t.reshape(n, l, heads, d).transpose(0, 2, 1, 3)
+    q, k, v = (split(f["x"] @ f["w" + s] + f["b" + s]) for s in "qkv")
+    scores = q @ k.transpose(0, 1, 3, 2) / np.float64(np.float32(np.sqrt(d))) + f["mask"]
+    p = softmax64(scores)
+    merged = (p @ v).transpose(0, 2, 1, 3).reshape(n, l, e)
+    o = merged @ f["wo"] + f["bo"] + f["x"]
+    h = np.maximum(o @ f["w1"] + f["b1"], 0)
+    out = h @ f["w2"] + f["b2"] + o
+    return dict(scores=scores, p=p, merged=merged, o=o, out=out)
+
+
+def block_inputs(rng, n, l, e, f):
+    a = {"x": rng.standard_normal((n, l, e)).astype(np.float32)}
+    for s in "qkvo":
+        a["w" + s] = (rng.standard_normal((e, e)) / np.sqrt(e)).astype(np.float32)
+        a["b" + s] = (rng.standard_normal(e) * 0.1).astype(np.float32)
+    a["w1"] = (rng.standard_normal((e, f)) / np.sqrt(e)).astype(np.float32)
+    a["b1"] = (rng.standard_normal(f) * 0.1).astype(np.float32)
+    a["w2"] = (rng.standard_normal((f, e)) / np.sqrt(f)).astype(np.float32)
+    a["b2"] = (rng.standard_normal(e) * 0.1).astype(np.float32)
+    mask = np.zeros((n, 1, 1, l), np.float32)
+    for i in range(n):  # ragged padding, as config 4 has it
+        mask[i, 0, 0, l - int(rng.integers(0, l // 4 + 1)):] = -100000.0
+    a["mask"] = mask
+    return a
+
+
+@pytest.mark.parametrize("n,l,e,heads,f", [(4, 96, 256, 4, 512), (2, 128, 768, 12, 3072), (3, 200, 128, 2, 320)])
+def test_transformer_block_lowered_vs_decomposed_vs_float64(n, l, e, heads, f):
+    a = block_inputs(np.random.default_rng(100 + l), n, l, e, f)
+    ref = attention_block64(a, heads)
+    lowered, plain = S.Context(0), S.Context(0, pattern_fusion=0)
+    try:
+        t1, _ = attention_block(lowered, a, heads)
+        t0, _ = attention_block(plain, a, heads)
+        names = list(t1)
+        lowered.eval(*[t1[k] for k in names])
+        plain.eval(*[t0[k] for k in names])
+        d = lowered.describe()
+        # the folds this test is about are really in the program
+        assert "gemm_grouped" in d and "slab(" in d            # q, k, v projections: one launch
+        assert "[store]" in d                                   # head merge
+        assert "gemm_batched{((x0 / sg_lit(" in d               # scale + mask in the scores epilogue
+        assert "softmax+planes" in d and "+planes" in d
+        dp = plain.describe()
+        assert "gemm{" not in dp and "[store]" not in dp and "gemm_grouped" not in dp and "+planes" not in dp
+        for k in names:
+            got, dec = lowered.read(t1[k]), plain.read(t0[k])
+            assert gemm_err(got, ref[k]) <= 1e-4, k
+            assert gemm_err(dec, ref[k]) <= 1e-4, k
+            assert gemm_err(got, dec) <= 1e-5, k
+        assert lowered.status_word() == 0 and plain.status_word() == 0
+    finally:
+        lowered.close()
+        plain.close()
+
+
+def test_rewriting_a_weight_invalidates_cached_planes_and_grouped_copies():
+    """Weights are split once and (for grouped launches) copied once; Var::set must make both stale."""
+    rng = np.random.default_rng(7)
+    a = block_inputs(rng, 2, 128, 256, 512)
+    ctx = S.Context(0)
+    try:
+        t, v = attention_block(ctx, a, 4)
+        ctx.eval(t["out"])
+        first = ctx.read(t["out"])
+        assert gemm_err(first, attention_block64(a, 4)["out"]) <= 1e-4
+        for name in ("wk", "bq", "w2"):
+            a[name] = (a[name] * np.float32(-0.5) + np.float32(0.01)).astype(np.float32)
+            ctx.set(v[name], a[name])
+        ctx.clear()
+        ctx.eval(t["out"])
+        second = ctx.read(t["out"])
+        assert gemm_err(second, attention_block64(a, 4)["out"]) <= 1e-4
+        assert gemm_err(second, first) > 1e-2  # and it did change
+    finally:
+        ctx.close()
+
+
+@pytest.mark.parametrize("m,n,k", [(130, 70, 147), (257, 36, 64), (64, 33, 32), (300, 513, 100)])
+def test_epilogue_on_ragged_shapes(m, n, k):
+    """N not a multiple of 4 (element-wise epilogue path), K with a row pitch TMA cannot address (operand
+    gathered into compact planes), tiles that hang over M and N."""
+    rng = np.random.default_rng(m * 1000 + n)
+    x = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    w = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    b = rng.uniform(-1, 1, (n,)).astype(np.float32)
+    r = rng.uniform(-1, 1, (m, n)).astype(np.float32)
+    col = rng.uniform(-1, 1, (m, 1)).astype(np.float32)
+    ctx = S.Context(0)
+    try:
+        X, W, B, Rr, C = (ctx.var(t) for t in (x, w, b, r, col))
+        y1 = S.relu(X.matmul(W) + B)
+        y2 = (X.matmul(W) + B) * C + Rr       # three epilogue operands: row vector, column vector, full tensor
+        y3 = (X.matmul(W) * 0.5).exp()
+        ctx.eval(y1, y2, y3)
+        d = ctx.describe()
+        assert d.count("gemm{") == 3
+        p = x.astype(np.float64) @ w.astype(np.float64)
+        assert gemm_err(ctx.read(y1), np.maximum(p + b, 0)) <= 1e-4
+        assert gemm_err(ctx.read(y2), (p + b) * col + r) <= 1e-4
+        assert gemm_err(ctx.read(y3), np.exp(p * 0.5)) <= 1e-4
+        assert ctx.status_word() == 0
+    finally:
+        ctx.close()
+
+
+def test_transposed_and_strided_operand_views():
+    """gemm(a^T), gemm over a sliced batch, and a product consumed by another product through a permute."""
+    rng = np.random.default_rng(11)
+    a = rng.uniform(-1, 1, (6, 96, 160)).astype(np.float32)
+    b = rng.uniform(-1, 1, (6, 96, 72)).astype(np.float32)
+    ctx = S.Context(0)
+    try:
+        A, B = ctx.var(a), ctx.var(b)
+        y = A.transpose(-1, -2).matmul_batched(B)                       # [6,160,96] x [6,96,72]: A read transposed
+        z = A.slice(0, 1, 5).transpose(-1, -2).matmul_batched(B.slice(0, 1, 5))
+        ctx.eval(y, z)
+        assert "map{(x0)}" not in ctx.describe()                        # no organize() copy survived
+        ref = np.einsum("bki,bkj->bij", a.astype(np.float64), b.astype(np.float64))
+        assert gemm_err(ctx.read(y), ref) <= 1e-4
+        assert gemm_err(ctx.read(z), ref[1:5]) <= 1e-4
+        assert ctx.status_word() == 0
+    finally:
+        ctx.close()
