@@ -82,6 +82,7 @@ struct Storage {
     std::shared_ptr<SplitCache> split;       // whole-storage planes
     std::shared_ptr<SplitCache> split_view;  // last compact split of a view
     uint64_t version = 0;                    // bumped whenever the contents are rewritten
+    bool planes_only = false;                // the fp32 buffer was never written: only `split` holds the value
     void drop_splits() {
         split.reset();
         split_view.reset();

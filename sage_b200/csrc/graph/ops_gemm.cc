@@ -127,6 +127,7 @@ static sage_status make_operand(Context &ctx, const Tensor &t, k::TcOperand *op,
         return SAGE_OK;
     }
     // Gather the view into compact planes (any strides; one pass instead of organize() + split).
+    if (st.planes_only) return ctx.fail(SAGE_ERR_INVALID, "internal: a planes-only tensor reached an operand TMA cannot address");
     if (!collapse_batch(sh, r - 2, &bl)) return ctx.fail(SAGE_ERR_UNSUPPORTED, "gemm: batch axes of an operand do not collapse to two levels");
     *swapped = false;
     std::shared_ptr<SplitCache> &c = st.split_view;
@@ -200,8 +201,8 @@ struct GemmOp : Operator {
     }
 
     sage_status compute(const std::vector<Tensor> &x, Context &ctx, Tensor *y) override {
-        const bool emit = ctx.hint_emit_planes;
-        ctx.hint_emit_planes = false;
+        const bool emit = ctx.hint_emit_planes, only = emit && ctx.hint_planes_only;
+        ctx.hint_emit_planes = ctx.hint_planes_only = false;
         sage_status st = Tensor::uninit(ctx, out, y);
         if (st) return st;
         if (!lowered) dims_from_inputs();
@@ -262,6 +263,10 @@ struct GemmOp : Operator {
             if (st) return st;
             g.c_hi = y->data->split->planes.planes + y->desc.shape.offset;
             g.c_plane = y->data->split->plane;
+            if (only) {
+                g.c = nullptr;
+                y->data->planes_only = true;
+            }
         }
         g.naux = naux();
         g.epilogue = epilogue;
@@ -467,6 +472,14 @@ std::shared_ptr<Operator> gemm_with_store(const Operator &op, const Shape &view,
 
 bool is_gemm_op(const Operator &op) { return as_gemm(op) != nullptr; }
 
+// Will operand `idx` be read straight from whole-storage planes (never through the fp32 buffer)?
+bool is_grouped_gemm_op(const Operator &op);
+bool gemm_operand_static_direct(const Operator &op, int idx) {
+    if (is_grouped_gemm_op(op)) return idx == 0 && gemm_operand_view_ok(op.in[0].shape);
+    const GemmOp *g = as_gemm(op);
+    return g && idx >= 0 && idx < 2 && gemm_operand_view_ok(g->in[idx].shape);
+}
+
 std::string describe_gemm(const Operator &op) {
     const GemmOp *g = as_gemm(op);
     if (!g) return "";
@@ -512,8 +525,8 @@ struct GroupedGemmOp : Operator {
     }
 
     sage_status compute(const std::vector<Tensor> &x, Context &ctx, Tensor *y) override {
-        const bool emit = ctx.hint_emit_planes;
-        ctx.hint_emit_planes = false;
+        const bool emit = ctx.hint_emit_planes, only = emit && ctx.hint_planes_only;
+        ctx.hint_emit_planes = ctx.hint_planes_only = false;
         sage_status st = Tensor::uninit(ctx, out, y);
         if (st) return st;
         const long long wsize = k * n;
@@ -587,6 +600,10 @@ struct GroupedGemmOp : Operator {
             if (st) return st;
             g.c_hi = y->data->split->planes.planes + y->desc.shape.offset;
             g.c_plane = y->data->split->plane;
+            if (only) {
+                g.c = nullptr;
+                y->data->planes_only = true;
+            }
         }
         g.epilogue = epilogue;
         if (has_bias) {

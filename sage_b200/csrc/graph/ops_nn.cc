@@ -26,8 +26,8 @@ struct RowOp : Operator {
     sage_status compute(const std::vector<Tensor> &x, Context &ctx, Tensor *y) override {
         if (!x[0].desc.shape.has_default_strides())
             return ctx.fail(SAGE_ERR_INVALID, std::string(name()) + ": input is not contiguous");
-        const bool emit = ctx.hint_emit_planes && kind != RLse;
-        ctx.hint_emit_planes = false;
+        const bool emit = ctx.hint_emit_planes && kind != RLse, only = emit && ctx.hint_planes_only;
+        ctx.hint_emit_planes = ctx.hint_planes_only = false;
         sage_status st = Tensor::uninit(ctx, out, y);
         if (st) return st;
         const float *xp = (const float *)x[0].ptr();
@@ -39,6 +39,10 @@ struct RowOp : Operator {
             if (st) return st;
             hi = y->data->split->planes.planes + y->desc.shape.offset;
             plane = y->data->split->plane;
+            if (only) {
+                yp = nullptr;
+                y->data->planes_only = true;
+            }
         }
         switch (kind) {
         case RSoftmax: return k::softmax_rows(ctx, xp, yp, rows, cols, hi, plane);

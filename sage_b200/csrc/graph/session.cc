@@ -25,6 +25,8 @@ struct Node {
     std::shared_ptr<Node> shared;  // a node several parents read (a grouped GEMM): evaluated once per routine run,
                                    // and passed to `op` as its only operand
     bool visited = false;          // traversal mark for shared nodes
+    bool planes_only = false;      // ... and that GEMM is the only reader: the fp32 result need not be stored
+    int readers = 0, gemm_readers = 0;  // shared nodes: how many parents, how many of them GEMM operands
 };
 
 // ops_map.cc / ops_core.cc / ops_gemm.cc / ops_nn.cc
@@ -41,6 +43,7 @@ std::shared_ptr<Operator> gemm_with_epilogue(const Operator &op, const std::stri
 std::shared_ptr<Operator> gemm_with_store(const Operator &op, const Shape &view, const TensorDesc &out, bool tc_enabled);
 bool row_op_emits_planes(const Operator &op);
 bool is_grouped_gemm_op(const Operator &op);
+bool gemm_operand_static_direct(const Operator &op, int idx);
 bool gemm_group_key(const Operator &op, std::string *key);
 std::shared_ptr<Operator> make_grouped_gemm(const std::vector<const Operator *> &members);
 std::shared_ptr<Operator> make_slab(const Operator &grouped, int index, const TensorDesc &member_out);
@@ -252,6 +255,7 @@ static void group_gemms(Node &root) {
             m->op = slab;
             m->args.clear();
             m->shared = shared;
+            ++shared->readers;
         }
     }
 }
@@ -271,6 +275,15 @@ static void mark_plane_readers(Node &n, bool tc, std::unordered_set<Origin *> *s
             if (p->var.is_op()) states->insert(p->var.key());
         } else if (can_emit_planes(*p->op, tc)) {
             p->emit_planes = true;
+            // Inside a routine's tree a node has one reader, so this GEMM is the only one — unless the
+            // node is shared (a grouped product): then every slab must end in a GEMM operand.
+            const bool direct = gemm_operand_static_direct(*n.op, idx);
+            if (p->readers > 0) {
+                if (direct) ++p->gemm_readers;
+                p->planes_only = p->gemm_readers == p->readers;
+            } else {
+                p->planes_only = direct;
+            }
         }
     }
 }
@@ -418,8 +431,9 @@ static sage_status run_node(const Node &n, Context &ctx, Session &s, const std::
         if (args[i].desc.shape.extents != n.op->in[i].shape.extents)
             return ctx.fail(SAGE_ERR_INVALID, std::string("operand extents differ from the operator's spec in ") + n.op->name());
     ctx.hint_emit_planes = n.emit_planes;
+    ctx.hint_planes_only = n.emit_planes && n.planes_only;
     sage_status st = n.op->compute(args, ctx, out);
-    ctx.hint_emit_planes = false;
+    ctx.hint_emit_planes = ctx.hint_planes_only = false;
     return st;
 }
 
@@ -553,7 +567,7 @@ static void describe_node(const Node &n, std::string *out) {
     out->append(n.op->name());
     if (const MapExpr *e = map_expr_of(*n.op)) out->append("{" + map_expr_text(*e) + "}");
     out->append(describe_gemm(*n.op));
-    if (n.emit_planes) out->append("+planes");
+    if (n.emit_planes) out->append(n.planes_only ? "=planes" : "+planes");
     out->push_back('(');
     if (n.shared) describe_node(*n.shared, out);
     for (size_t i = 0; i < n.args.size(); ++i) {

@@ -47,7 +47,7 @@ struct RowParams {
 };
 
 __device__ __forceinline__ void row_store4(const RowParams &p, long long at, float4 o) {
-    *reinterpret_cast<float4 *>(p.y + at) = o;
+    if (p.y) *reinterpret_cast<float4 *>(p.y + at) = o;  // y is null when only the planes are wanted
     if (p.hi) {
         float4 h, l;
         sage_tc::split_tf32_value(o.x, &h.x, &l.x);
@@ -59,7 +59,7 @@ __device__ __forceinline__ void row_store4(const RowParams &p, long long at, flo
     }
 }
 __device__ __forceinline__ void row_store1(const RowParams &p, long long at, float o) {
-    p.y[at] = o;
+    if (p.y) p.y[at] = o;
     if (p.hi) {
         float h, l;
         sage_tc::split_tf32_value(o, &h, &l);

@@ -145,6 +145,8 @@ public:
     // Set by the evaluator around one operator's compute(): a tensor-core GEMM will read the result,
     // so a producer that can should also write the tf32 hi/lo planes of what it computes.
     bool hint_emit_planes = false;
+    // ... and nothing else reads it: the producer may skip the fp32 store and write only the planes.
+    bool hint_planes_only = false;
     int sm_count = 148;
 
 private:

@@ -234,13 +234,14 @@ def test_bert_base_plan():
     # GEMMs; what is left is the embedding sum, the per-layer mask bias and the classifier's two maps
     assert t.count("sage_map") == 1 + 12 + 2
     d = c.describe()
-    # the three projections of a layer input are one grouped launch, read back as three slabs
-    assert d.count("slab(gemm_grouped+planes(") == 36
-    assert d.count("gemm_batched[store]+planes") == 12                       # head merge = store pattern of P.V
+    # the three projections of a layer input are one grouped launch, read back as three slabs;
+    # "=planes": the only reader is a GEMM, so the fp32 result is not stored at all
+    assert d.count("slab(gemm_grouped=planes(") == 36
+    assert d.count("gemm_batched[store]=planes") == 12                       # head merge = store pattern of P.V
     assert d.count("gemm_batched{((x0 / sg_lit(0x41000000u)) + x1)}") == 12  # scores: scale + mask in the epilogue
-    assert d.count("gemm{(((float)((x0 + x1) > sg_lit(0x00000000u))) * (x0 + x1))}+planes") == 12  # FFN up: bias + relu
+    assert d.count("gemm{(((float)((x0 + x1) > sg_lit(0x00000000u))) * (x0 + x1))}=planes") == 12  # FFN up: bias + relu
     assert d.count("gemm{((x0 + x1) + x2)}") == 24                           # output / FFN down: bias + residual
-    assert d.count("softmax+planes") == 12 and d.count("layer_norm+planes") == 24
+    assert d.count("softmax=planes") == 12 and d.count("layer_norm+planes") == 24  # layer norm also feeds the residual
     assert c.mem_stats()["mem_peak"] < 3 << 30
     c.close()
 
