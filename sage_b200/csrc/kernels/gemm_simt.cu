@@ -107,11 +107,33 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(GemmP p) {
         }
     }
 }
+// Few outputs, long K (a classifier head: 32 x 2 outputs, K = 768): one warp per output element,
+// the lanes share K, so the tile kernel's single CTA walking K alone is avoided.
+__global__ void __launch_bounds__(256) gemm_skinny_kernel(GemmP p, long long sai, long long sak, long long sbk, long long sbj) {
+    const int lane = threadIdx.x & 31;
+    const long long out = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long per_batch = p.m * p.n;
+    if (out >= per_batch * (long long)gridDim.y) return;
+    const long long i = out / p.n, j = out % p.n;
+    const float *A = p.a + (long long)blockIdx.y * p.sa + i * sai;
+    const float *B = p.b + (long long)blockIdx.y * p.sb + j * sbj;
+    float acc = 0.f;
+    for (long long kk = lane; kk < p.k; kk += 32) acc = fmaf(A[kk * sak], B[kk * sbk], acc);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0 && out < per_batch) p.c[(long long)blockIdx.y * p.sc + i * p.ldc + j] = acc;
+}
 }  // namespace
 
 sage_status gemm_simt(Context &ctx, const GemmArgs &g) {
     ctx.note_launch("gemm_simt");
     if (ctx.dry() || g.m == 0 || g.n == 0 || g.batch == 0) return SAGE_OK;
+    if (g.m * g.n <= 8192 && g.k >= 128 && g.batch <= 65535) {
+        GemmP p{g.m, g.n, g.k, g.a, g.lda, g.stride_a, g.b, g.ldb, g.stride_b, g.c, g.ldc, g.stride_c};
+        const dim3 grid((unsigned)((g.m * g.n + 7) / 8), (unsigned)g.batch);
+        gemm_skinny_kernel<<<grid, 256, 0, ctx.stream()>>>(p, g.ta ? 1 : g.lda, g.ta ? g.lda : 1, g.tb ? 1 : g.ldb, g.tb ? g.ldb : 1);
+        return ctx.check_cuda(cudaGetLastError(), "gemm_skinny launch");
+    }
     GemmP p{g.m, g.n, g.k, g.a, g.lda, g.stride_a, g.b, g.ldb, g.stride_b, g.c, g.ldc, g.stride_c};
     dim3 grid((unsigned)((g.n + BN - 1) / BN), (unsigned)((g.m + BM - 1) / BM), (unsigned)g.batch);
     if (grid.y > 65535 || grid.z > 65535) return ctx.fail(SAGE_ERR_UNSUPPORTED, "gemm_simt: grid too large");

@@ -1,0 +1,128 @@
+"""BASELINE configs 4 and 5 at their full sizes.  The CPU oracle cannot evaluate them in reasonable
+time, so the full batch is checked through properties that do not depend on size:
+
+  * a forward pass is independent per sample, and every output element is accumulated in the same
+    order whatever the batch, so the first rows of the full-batch result must equal — bit for bit —
+    the result of evaluating those samples alone;
+  * shuffling the batch shuffles the outputs (again bit for bit);
+  * the small batch itself is compared with the oracle (rel <= 1e-3 on logits).
+
+Config 4 is the BERT-large-shaped graph (24 layers, width 1024, 16 heads, FFN 4096, L 512, batch 256,
+ragged padding 0-128 per sequence); config 5 is sage's ResNet-18 graph on [256, 224, 224, 3].
+Weights and inputs are seeded synthetic tensors with the distributions BASELINE.json states.
+"""
+import time
+
+import numpy as np
+import pytest
+
+import sage_b200 as S
+from oracle import sage_ref as R
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(a, b, floor):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    scale = np.maximum(np.abs(b), floor * max(np.abs(b).max(), 1e-30))
+    return float((np.abs(a - b) / scale).max())
+
+
+def RV(a, dtype=None):
+    return R.Var.new(R.Tensor.new(a, dtype))
+
+
+LARGE = dict(embed_dim=1024, num_vocabs=30522, max_num_tokens=512, hidden_dim=4096, num_layers=24, num_heads=16, num_classes=2)
+
+
+def test_config4_bert_large_full_batch():
+    rng = np.random.default_rng(4001)
+    batch, seq = 256, 512
+    ctx = S.Context(0)
+    try:
+        model = S.Bert(**LARGE)
+        params = model.params()
+        values = [(rng.standard_normal(p.extents) * 0.02).astype(np.float32) for p in params]
+        for p, v in zip(params, values):
+            ctx.set(p, v)
+        ids = rng.integers(0, 30522, (batch, seq)).astype(np.uint32)
+        mask = np.ones((batch, seq), np.float32)
+        for i, pad in enumerate(rng.integers(0, 129, batch)):
+            mask[i, seq - pad:] = 0
+
+        def run(rows):
+            t0 = time.perf_counter()
+            out = model.pass_(ctx.var(ids[rows]), ctx.var(mask[rows])).eval(ctx)
+            ctx.sync()
+            return out, time.perf_counter() - t0
+        full, _ = run(np.arange(batch))
+        full2, dt = run(np.arange(batch))  # second pass: weights split, kernels compiled
+        print("\nconfig 4: %d sequences in %.3f s = %.1f seq/s, peak memory %.1f GB" %
+              (batch, dt, batch / dt, ctx.mem_stats()["mem_peak"] / 1e9))
+        assert full.shape == (batch, 2) and np.isfinite(full).all() and np.array_equal(full, full2)
+        small, _ = run(np.arange(2))
+        assert np.array_equal(full[:2], small)                      # per-sample independence, bit for bit
+        perm = rng.permutation(batch)
+        shuffled, _ = run(perm)
+        assert np.array_equal(shuffled, full[perm])                 # batch order does not matter
+        assert ctx.status_word() == 0
+        # the two-sequence batch against the oracle (one layer stack of 24 on the host cores)
+        rm = R.Bert(R.BertConfig(embed_dim=1024, num_vocabs=30522, max_num_tokens=512, hidden_dim=4096, num_layers=24,
+                                 num_heads=16, num_classes=2))
+        for p, v in zip(rm.params(), values):
+            p.set(v)
+        ref = rm(RV(ids[:2], R.UINT), RV(mask[:2])).eval().numpy()
+        assert rel_err(small, ref, floor=1e-3) <= 1e-3
+    finally:
+        ctx.close()
+
+
+def test_config5_resnet18_full_batch():
+    rng = np.random.default_rng(5001)
+    batch = 256
+    ctx = S.Context(0)
+    try:
+        model = S.ResNet18(3, 1000)
+        params = model.params()
+        values = []
+        for p in params:
+            e = p.extents
+            if len(e) == 4:    # conv filter [KH, KW, C, OC]: He-normal
+                values.append((rng.standard_normal(e) * np.sqrt(2.0 / (e[0] * e[1] * e[2]))).astype(np.float32))
+            elif len(e) == 2:  # classifier
+                values.append((rng.standard_normal(e) * np.sqrt(1.0 / e[0])).astype(np.float32))
+            else:
+                values.append(np.zeros(e, np.float32))
+        for p, v in zip(params, values):
+            ctx.set(p, v)
+        x = rng.standard_normal((batch, 224, 224, 3)).astype(np.float32)
+
+        def run(rows):
+            t0 = time.perf_counter()
+            out = model.pass_(ctx.var(x[rows])).eval(ctx)
+            ctx.sync()
+            return out, time.perf_counter() - t0
+        full, _ = run(np.arange(batch))
+        full2, dt = run(np.arange(batch))
+        print("\nconfig 5: %d images in %.3f s = %.1f img/s, peak memory %.1f GB" %
+              (batch, dt, batch / dt, ctx.mem_stats()["mem_peak"] / 1e9))
+        assert full.shape == (batch, 1000) and np.isfinite(full).all() and np.array_equal(full, full2)
+        # 64 samples keep every contraction on the tensor-core kernel (the classifier has M = batch), so
+        # the arithmetic per element is the same as in the full batch
+        part, _ = run(np.arange(64))
+        assert np.array_equal(full[:64], part)
+        perm = rng.permutation(batch)
+        shuffled, _ = run(perm)
+        assert np.array_equal(shuffled, full[perm])
+        assert ctx.status_word() == 0
+        small, _ = run(np.arange(2))
+        # batch 2 sends the classifier (M = batch) to the SIMT kernel: other summation order, same values
+        # (a contraction's error is measured against the rms of its outputs)
+        assert float(np.abs(small - full[:2]).max() / np.sqrt((full[:2].astype(np.float64) ** 2).mean())) <= 1e-5
+        rm = R.resnet18(3, 1000)
+        for p, v in zip(rm.params(), values):
+            p.set(v)
+        ref = rm(RV(x[:2])).eval().numpy()
+        assert rel_err(small, ref, floor=1e-3) <= 1e-3
+    finally:
+        ctx.close()

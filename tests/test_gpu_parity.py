@@ -321,6 +321,24 @@ def test_gemm_transposes_vs_oracle(ctx, ta, tb):
     assert gemm_err(got, ref) <= 1e-4
 
 
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_skinny_gemm_vs_oracle(ctx, ta, tb):
+    """Few outputs, long K (the classifier head's shape): the warp-per-output kernel."""
+    rng = np.random.default_rng(2004)
+    m, n, k = 32, 3, 771
+    a = rng.uniform(-1, 1, (k, m) if ta else (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (n, k) if tb else (k, n)).astype(np.float32)
+    ctx.trace_begin()
+    got = S.gemm(ctx.var(a), ctx.var(b), ta, tb).eval(ctx)
+    assert "gemm_simt" in ctx.trace()
+    ref = R.gemm(RV(a), RV(b), bool(ta), bool(tb)).eval().numpy()
+    assert gemm_err(got, ref) <= 1e-4
+    a3 = rng.uniform(-1, 1, (5, 8, 300)).astype(np.float32)
+    b3 = rng.uniform(-1, 1, (5, 300, 2)).astype(np.float32)
+    got = S.matmul_batched(ctx.var(a3), ctx.var(b3)).eval(ctx)
+    assert gemm_err(got, a3.astype(np.float64) @ b3.astype(np.float64)) <= 1e-4
+
+
 @pytest.mark.parametrize("sa,sb", [((16, 512, 64), (16, 64, 512)), ((16, 512, 512), (16, 512, 64)), ((3, 5, 7), (3, 7, 2))])
 def test_batch_matmul_vs_oracle(ctx, sa, sb):
     rng = np.random.default_rng(2003)
