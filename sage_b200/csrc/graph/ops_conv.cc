@@ -30,6 +30,20 @@ struct Im2colOp : Operator {
     }
 };
 
+bool im2col_params(const Operator &op, k::Window *w, long long dims[6]) {
+    const Im2colOp *o = dynamic_cast<const Im2colOp *>(&op);
+    if (!o || o->in[0].dtype != SAGE_F32 || !o->in[0].shape.has_default_strides()) return false;
+    *w = window(o->ker, o->stride, o->pad, o->dil);
+    const Array &e = o->in[0].shape.extents;
+    dims[0] = e[0];
+    dims[1] = e[1];
+    dims[2] = e[2];
+    dims[3] = e[3];
+    dims[4] = o->col.h;
+    dims[5] = o->col.w;
+    return true;
+}
+
 struct Col2imOp : Operator {
     Pair img, ker, stride, pad, dil;
     const char *name() const override { return "col2im"; }

@@ -174,6 +174,9 @@ struct GemmOp : Operator {
     std::string epilogue;           // C expression over x0 (the product) and x1.. (inputs 2..)
     Array epi_ext;                  // extents of the epilogue operands (the fused map's index space)
     std::vector<int> epi_group;     // per axis of epi_ext: GBatchHi .. GCol
+    bool conv = false;              // operand A is the im2col of input 0 ([N,H,W,C]), made on the fly as tf32 planes
+    k::Window win{};
+    long long img[6] = {0, 0, 0, 0, 0, 0};  // N, H, W, C, OH, OW
     bool folded = false;            // result stored through (ldc, sc0, sc1, nbc0) instead of row-major [batch, M, N]
     long long ldc = 0, sc0 = 0, sc1 = 0, nbc0 = 1;
 
@@ -234,8 +237,35 @@ struct GemmOp : Operator {
         g.batch = batch;
         std::shared_ptr<SplitCache> hold_a, hold_b;
         bool sw_a = false, sw_b = false;
-        st = make_operand(ctx, x[0], &g.a, &sw_a, &hold_a);
-        if (st) return st;
+        Block *col_block = nullptr;  // conv: the column matrix exists only as tf32 planes, only for this launch
+        if (conv) {
+            if (!x[0].desc.shape.has_default_strides() || ta) return ctx.fail(SAGE_ERR_INVALID, "internal: conv gemm needs a contiguous image");
+            const int pitch = (int)((k + 3) / 4 * 4);
+            const long long plane = m * pitch;
+            col_block = ctx.allocator().alloc((size_t)plane * 2 * sizeof(float));
+            if (!col_block) return ctx.fail(SAGE_ERR_OOM, "out of memory for the convolution's column planes");
+            float *hi = reinterpret_cast<float *>(col_block->ptr);
+            st = k::im2col_planes(ctx, (const float *)x[0].ptr(), img[0], img[1], img[2], img[3], img[4], img[5], win, nullptr, hi, plane, pitch);
+            if (st) {
+                ctx.allocator().free(col_block);
+                return st;
+            }
+            g.a.hi = hi;
+            g.a.plane = plane;
+            g.a.ld = pitch;
+            g.a.rows = m;
+            g.a.cols = k;
+        } else {
+            st = make_operand(ctx, x[0], &g.a, &sw_a, &hold_a);
+            if (st) return st;
+        }
+        struct FreeCol {  // stream-ordered: the block may be reused by launches enqueued after the GEMM
+            Context &c;
+            Block *b;
+            ~FreeCol() {
+                if (b) c.allocator().free(b);
+            }
+        } free_col{ctx, col_block};
         st = make_operand(ctx, x[1], &g.b, &sw_b, &hold_b);
         if (st) return st;
         // A lies as [M,K] (K contiguous) unless transposed; B as [K,N] (N contiguous) unless transposed.
@@ -362,6 +392,7 @@ static std::shared_ptr<GemmOp> lowered_clone(const GemmOp &g) {
 std::shared_ptr<Operator> gemm_with_operand_view(const Operator &op, int idx, const TensorDesc &view, bool tc_enabled) {
     const GemmOp *g = as_gemm(op);
     if (!g || idx < 0 || idx > 1 || view.dtype != SAGE_F32 || !gemm_runs_on_tc(op, tc_enabled)) return nullptr;
+    if (g->conv && idx == 0) return nullptr;  // input 0 is the image, which im2col reads contiguous
     auto c = lowered_clone(*g);
     const Shape &old = c->in[idx].shape, &sh = view.shape;
     const int r = sh.rank(), ro = old.rank();
@@ -472,11 +503,29 @@ std::shared_ptr<Operator> gemm_with_store(const Operator &op, const Shape &view,
 
 bool is_gemm_op(const Operator &op) { return as_gemm(op) != nullptr; }
 
+// gemm(reshape(im2col(x)), W): the column matrix is never stored as fp32 — the GEMM makes its tf32
+// planes straight from the image (one pass instead of im2col + split, a third of the traffic).
+bool im2col_params(const Operator &op, k::Window *w, long long dims[6]);  // ops_conv.cc
+std::shared_ptr<Operator> gemm_with_im2col(const Operator &op, const Operator &im2col_op, bool tc_enabled) {
+    const GemmOp *g = as_gemm(op);
+    k::Window w;
+    long long d[6];
+    if (!g || g->ta || g->conv || !gemm_runs_on_tc(op, tc_enabled) || !im2col_params(im2col_op, &w, d)) return nullptr;
+    auto c = lowered_clone(*g);
+    if (c->batch != 1 || c->m != d[0] * d[4] * d[5] || c->k != (long long)w.ker_h * w.ker_w * d[3]) return nullptr;
+    c->conv = true;
+    c->win = w;
+    for (int i = 0; i < 6; ++i) c->img[i] = d[i];
+    c->in[0] = im2col_op.in[0];
+    return c;
+}
+
 // Will operand `idx` be read straight from whole-storage planes (never through the fp32 buffer)?
 bool is_grouped_gemm_op(const Operator &op);
 bool gemm_operand_static_direct(const Operator &op, int idx) {
     if (is_grouped_gemm_op(op)) return idx == 0 && gemm_operand_view_ok(op.in[0].shape);
     const GemmOp *g = as_gemm(op);
+    if (g && g->conv && idx == 0) return false;  // the image is read by im2col, as fp32
     return g && idx >= 0 && idx < 2 && gemm_operand_view_ok(g->in[idx].shape);
 }
 
@@ -484,6 +533,7 @@ std::string describe_gemm(const Operator &op) {
     const GemmOp *g = as_gemm(op);
     if (!g) return "";
     std::string s;
+    if (g->conv) s += "<im2col>";
     if (!g->epilogue.empty()) s += "{" + g->epilogue + "}";
     if (g->folded) s += "[store]";
     return s;
@@ -636,7 +686,7 @@ bool is_grouped_gemm_op(const Operator &op) { return dynamic_cast<const GroupedG
 // (same A view, same shape and transposes, same epilogue text); the caller adds A's identity.
 bool gemm_group_key(const Operator &op, std::string *key) {
     const GemmOp *g = as_gemm(op);
-    if (!g || !g->lowered || g->folded || g->batch != 1 || g->naux() > 1) return false;
+    if (!g || !g->lowered || g->folded || g->conv || g->batch != 1 || g->naux() > 1) return false;
     if (g->n % 4 || g->k % 4 || !g->in[1].shape.has_default_strides() || g->in[1].shape.rank() != 2) return false;
     if (g->naux() == 1) {  // the one epilogue operand must be a row vector broadcast over the rows
         const Shape &b = g->in[2].shape;

@@ -40,6 +40,7 @@ bool gemm_can_fuse(const Operator &op, bool tc_enabled);
 std::shared_ptr<Operator> gemm_with_operand_view(const Operator &op, int idx, const TensorDesc &view, bool tc_enabled);
 std::shared_ptr<Operator> gemm_with_epilogue(const Operator &op, const std::string &expr, const std::vector<TensorDesc> &aux,
                                              const TensorDesc &out);
+std::shared_ptr<Operator> gemm_with_im2col(const Operator &op, const Operator &im2col_op, bool tc_enabled);
 std::shared_ptr<Operator> gemm_with_store(const Operator &op, const Shape &view, const TensorDesc &out, bool tc_enabled);
 bool row_op_emits_planes(const Operator &op);
 bool is_grouped_gemm_op(const Operator &op);
@@ -140,6 +141,18 @@ static void lower(Node &n, bool tc) {
     for (Node &a : n.args) lower(a, tc);
     // operands behind an organize() copy
     if (is_gemm_op(*n.op) && gemm_runs_on_tc(*n.op, tc)) {
+        {  // the column matrix of a convolution: made by the GEMM itself, as planes
+            Node *p = &n.args[0];
+            while (!p->is_data && is_reshape_op(*p->op)) p = &p->args[0];
+            if (!p->is_data && p != &n.args[0] && p->args.size() == 1) {
+                std::shared_ptr<Operator> f = gemm_with_im2col(*n.op, *p->op, tc);
+                if (f) {
+                    Node inner = std::move(p->args[0]);
+                    n.args[0] = std::move(inner);
+                    n.op = f;
+                }
+            }
+        }
         for (int idx = 0; idx < 2; ++idx) {
             Node *p = &n.args[idx];
             while (!p->is_data && is_reshape_op(*p->op) && reshape_keeps_matrix(*p->op)) p = &p->args[0];
@@ -272,12 +285,12 @@ static void mark_plane_readers(Node &n, bool tc, std::unordered_set<Origin *> *s
     for (int idx = 0; idx < (grouped ? 1 : 2); ++idx) {
         Node *p = skip_views(&n.args[idx]);
         if (p->is_data) {
-            if (p->var.is_op()) states->insert(p->var.key());
+            if (p->var.is_op() && gemm_operand_static_direct(*n.op, idx)) states->insert(p->var.key());
         } else if (can_emit_planes(*p->op, tc)) {
-            p->emit_planes = true;
             // Inside a routine's tree a node has one reader, so this GEMM is the only one — unless the
             // node is shared (a grouped product): then every slab must end in a GEMM operand.
             const bool direct = gemm_operand_static_direct(*n.op, idx);
+            if (direct) p->emit_planes = true;
             if (p->readers > 0) {
                 if (direct) ++p->gemm_readers;
                 p->planes_only = p->gemm_readers == p->readers;

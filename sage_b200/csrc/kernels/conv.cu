@@ -7,9 +7,11 @@
 // (conv.rs:143-165: im2col, then a reduction over [KH,KW]) straight from the image without
 // materialising the KH*KW-times larger column tensor.  Padded taps count as zeros, and with
 // ref_compat the max starts from 0 like the reference's reduce accumulator.
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include "kernels.h"
+#include "gemm_tc_device.inc"  // split_tf32_value
 
 namespace sage {
 namespace k {
@@ -19,22 +21,70 @@ struct ConvP {
     Window w;
 };
 
-__global__ void __launch_bounds__(256) im2col_kernel(const float *__restrict__ img, float *__restrict__ col, ConvP p,
-                                                     long long total) {
-    for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < total;
-         g += (long long)gridDim.x * blockDim.x) {
-        long long r = g;
-        const long long c = r % p.chan; r /= p.chan;
-        const long long kx = r % p.w.ker_w; r /= p.w.ker_w;
-        const long long ky = r % p.w.ker_h; r /= p.w.ker_h;
-        const long long ox = r % p.col_w; r /= p.col_w;
-        const long long oy = r % p.col_h; r /= p.col_h;
-        const long long n = r;
-        const long long iy = oy * p.w.stride_h - p.w.pad_h + ky * p.w.dil_h;
-        const long long ix = ox * p.w.stride_w - p.w.pad_w + kx * p.w.dil_w;
-        float v = 0.f;
-        if (ix >= 0 && ix < p.img_w && iy >= 0 && iy < p.img_h) v = img[((n * p.img_h + iy) * p.img_w + ix) * p.chan + c];
-        col[g] = v;
+// One warp per output pixel: the K = KH*KW*C values of a column row are contiguous in the output and
+// C-contiguous runs in the image, so with C % 4 == 0 the lanes move 16-byte chunks and both sides
+// coalesce; index arithmetic is 32-bit per chunk and once per pixel.  Outputs: the fp32 column
+// tensor (row pitch K) and / or the tf32 hi / lo planes of it (row pitch `pitch` >= K, a multiple of
+// 4; pad columns are written as zeros) for the tensor-core GEMM that consumes it.
+struct ColOut {
+    float *col;       // may be null
+    float *hi;        // may be null; lo = hi + plane
+    long long plane;
+    int pitch;
+};
+
+__device__ __forceinline__ void split_pair(float x, float *hi, float *lo) { sage_tc::split_tf32_value(x, hi, lo); }
+
+__global__ void __launch_bounds__(256) im2col_kernel(const float *__restrict__ img, ColOut o, ConvP p, long long pixels) {
+    const int lane = threadIdx.x & 31;
+    const long long pix = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (pix >= pixels) return;
+    const unsigned per_img = (unsigned)(p.col_h * p.col_w);
+    const long long n = pix / per_img;
+    const unsigned r = (unsigned)(pix - n * per_img);
+    const int oy = (int)(r / (unsigned)p.col_w), ox = (int)(r % (unsigned)p.col_w);
+    const int iy0 = oy * p.w.stride_h - p.w.pad_h, ix0 = ox * p.w.stride_w - p.w.pad_w;
+    const int C = (int)p.chan, K = p.w.ker_h * p.w.ker_w * C;
+    const float *im = img + n * p.img_h * p.img_w * C;
+    if ((C & 3) == 0) {
+        const int c4n = C >> 2, chunks = K >> 2;
+        for (int ch = lane; ch < chunks; ch += 32) {
+            const int tap = ch / c4n, c = (ch - tap * c4n) << 2;
+            const int ky = tap / p.w.ker_w, kx = tap - ky * p.w.ker_w;
+            const int iy = iy0 + ky * p.w.dil_h, ix = ix0 + kx * p.w.dil_w;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (ix >= 0 && ix < p.img_w && iy >= 0 && iy < p.img_h)
+                v = __ldg(reinterpret_cast<const float4 *>(im + ((long long)iy * p.img_w + ix) * C + c));
+            if (o.col) *reinterpret_cast<float4 *>(o.col + pix * K + (ch << 2)) = v;
+            if (o.hi) {
+                float4 h, l;
+                split_pair(v.x, &h.x, &l.x);
+                split_pair(v.y, &h.y, &l.y);
+                split_pair(v.z, &h.z, &l.z);
+                split_pair(v.w, &h.w, &l.w);
+                float *d = o.hi + pix * o.pitch + (ch << 2);
+                *reinterpret_cast<float4 *>(d) = h;
+                *reinterpret_cast<float4 *>(d + o.plane) = l;
+            }
+        }
+    } else {
+        const int width = o.hi ? o.pitch : K;
+        for (int kk = lane; kk < width; kk += 32) {
+            float v = 0.f;
+            if (kk < K) {
+                const int tap = kk / C, c = kk - tap * C;
+                const int ky = tap / p.w.ker_w, kx = tap - ky * p.w.ker_w;
+                const int iy = iy0 + ky * p.w.dil_h, ix = ix0 + kx * p.w.dil_w;
+                if (ix >= 0 && ix < p.img_w && iy >= 0 && iy < p.img_h) v = __ldg(im + ((long long)iy * p.img_w + ix) * C + c);
+                if (o.col) o.col[pix * K + kk] = v;
+            }
+            if (o.hi) {
+                float h, l;
+                split_pair(v, &h, &l);
+                o.hi[pix * o.pitch + kk] = h;
+                o.hi[pix * o.pitch + kk + o.plane] = l;
+            }
+        }
     }
 }
 
@@ -70,28 +120,51 @@ __global__ void __launch_bounds__(256) col2im_kernel(const float *__restrict__ c
     }
 }
 
+// One thread per output pixel and group of 4 channels when C % 4 == 0 (16-byte loads, one 64-bit
+// division per thread), else one thread per element.
+template <int VEC>
 __global__ void __launch_bounds__(256) pool2d_kernel(const float *__restrict__ img, float *__restrict__ out, ConvP p,
                                                      long long total, int is_max, int ref_compat) {
+    const unsigned cn = (unsigned)(p.chan / VEC);
     for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < total;
          g += (long long)gridDim.x * blockDim.x) {
-        long long r = g;
-        const long long c = r % p.chan; r /= p.chan;
-        const long long ox = r % p.col_w; r /= p.col_w;
-        const long long oy = r % p.col_h; r /= p.col_h;
-        const long long n = r;
-        float acc = is_max ? (ref_compat ? 0.f : -INFINITY) : 0.f;
+        const long long pix = g / cn;
+        const int c = (int)(g - pix * cn) * VEC;
+        const unsigned per_img = (unsigned)(p.col_h * p.col_w);
+        const long long n = pix / per_img;
+        const unsigned r = (unsigned)(pix - n * per_img);
+        const int oy = (int)(r / (unsigned)p.col_w), ox = (int)(r % (unsigned)p.col_w);
+        const float init = is_max ? (ref_compat ? 0.f : -INFINITY) : 0.f;
+        float acc[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) acc[j] = init;
         // reduce over axes [3,4] = [KH,KW]: the first listed axis (KH) is the inner loop
         for (int kx = 0; kx < p.w.ker_w; ++kx)
             for (int ky = 0; ky < p.w.ker_h; ++ky) {
-                const long long iy = oy * p.w.stride_h - p.w.pad_h + (long long)ky * p.w.dil_h;
-                const long long ix = ox * p.w.stride_w - p.w.pad_w + (long long)kx * p.w.dil_w;
-                float v = 0.f;
-                if (ix >= 0 && ix < p.img_w && iy >= 0 && iy < p.img_h)
-                    v = img[((n * p.img_h + iy) * p.img_w + ix) * p.chan + c];
-                acc = is_max ? fmaxf(acc, v) : acc + v;
+                const int iy = oy * p.w.stride_h - p.w.pad_h + ky * p.w.dil_h;
+                const int ix = ox * p.w.stride_w - p.w.pad_w + kx * p.w.dil_w;
+                float v[VEC];
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) v[j] = 0.f;
+                if (ix >= 0 && ix < p.img_w && iy >= 0 && iy < p.img_h) {
+                    const float *src = img + ((n * p.img_h + iy) * p.img_w + ix) * p.chan + c;
+                    if (VEC == 4) {
+                        const float4 t = __ldg(reinterpret_cast<const float4 *>(src));
+                        v[0] = t.x; v[1 % VEC] = t.y; v[2 % VEC] = t.z; v[3 % VEC] = t.w;
+                    } else {
+                        v[0] = __ldg(src);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) acc[j] = is_max ? fmaxf(acc[j], v[j]) : acc[j] + v[j];
             }
-        if (!is_max) acc = acc / (float)(p.w.ker_w * p.w.ker_h);
-        out[g] = acc;
+        if (!is_max) {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) acc[j] = acc[j] / (float)(p.w.ker_w * p.w.ker_h);
+        }
+        float *dst = out + pix * p.chan + c;
+        if (VEC == 4) *reinterpret_cast<float4 *>(dst) = make_float4(acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]);
+        else dst[0] = acc[0];
     }
 }
 
@@ -101,14 +174,27 @@ static unsigned grid_for(Context &ctx, long long n) {
     return (unsigned)(blocks < cap ? blocks : cap);
 }
 
+sage_status im2col_planes(Context &ctx, const float *img, long long n, long long img_h, long long img_w, long long chan,
+                          long long col_h, long long col_w, const Window &w, float *col, float *hi, long long plane, int pitch) {
+    ConvP p{n, img_h, img_w, chan, col_h, col_w, w};
+    const long long pixels = n * col_h * col_w;
+    ctx.note_launch("im2col");
+    if (ctx.dry() || pixels == 0) return SAGE_OK;
+    if (col_h * col_w > 0x7fffffffLL || img_h > 0x7fffffffLL || img_w > 0x7fffffffLL || (long long)w.ker_h * w.ker_w * chan > 0x7fffffffLL ||
+        (pixels + 7) / 8 > 0x7fffffffLL)
+        return ctx.fail(SAGE_ERR_UNSUPPORTED, "im2col: extents beyond 2^31");
+    const bool vec = chan % 4 == 0;
+    if (vec && ((col && reinterpret_cast<uintptr_t>(col) % 16) || reinterpret_cast<uintptr_t>(img) % 16 ||
+                (hi && (reinterpret_cast<uintptr_t>(hi) % 16 || plane % 4 || pitch % 4))))
+        return ctx.fail(SAGE_ERR_INVALID, "im2col: unaligned buffer");
+    ColOut o{col, hi, plane, pitch};
+    im2col_kernel<<<(unsigned)((pixels + 7) / 8), 256, 0, ctx.stream()>>>(img, o, p, pixels);
+    return ctx.check_cuda(cudaGetLastError(), "im2col launch");
+}
+
 sage_status im2col(Context &ctx, const float *img, float *col, long long n, long long img_h, long long img_w,
                    long long chan, long long col_h, long long col_w, const Window &w) {
-    ConvP p{n, img_h, img_w, chan, col_h, col_w, w};
-    long long total = n * col_h * col_w * w.ker_h * w.ker_w * chan;
-    ctx.note_launch("im2col");
-    if (ctx.dry() || total == 0) return SAGE_OK;
-    im2col_kernel<<<grid_for(ctx, total), 256, 0, ctx.stream()>>>(img, col, p, total);
-    return ctx.check_cuda(cudaGetLastError(), "im2col launch");
+    return im2col_planes(ctx, img, n, img_h, img_w, chan, col_h, col_w, w, col, nullptr, 0, 0);
 }
 
 sage_status col2im(Context &ctx, const float *col, float *img, long long n, long long img_h, long long img_w,
@@ -127,7 +213,10 @@ sage_status pool2d(Context &ctx, bool is_max, const float *img, float *out, long
     long long total = n * out_h * out_w * chan;
     ctx.note_launch(is_max ? "max_pool2d" : "avg_pool2d");
     if (ctx.dry() || total == 0) return SAGE_OK;
-    pool2d_kernel<<<grid_for(ctx, total), 256, 0, ctx.stream()>>>(img, out, p, total, is_max ? 1 : 0, ctx.opts().ref_compat);
+    const bool vec = chan % 4 == 0 && reinterpret_cast<uintptr_t>(img) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
+                     out_h * out_w <= 0x7fffffffLL;
+    if (vec) pool2d_kernel<4><<<grid_for(ctx, total / 4), 256, 0, ctx.stream()>>>(img, out, p, total / 4, is_max ? 1 : 0, ctx.opts().ref_compat);
+    else pool2d_kernel<1><<<grid_for(ctx, total), 256, 0, ctx.stream()>>>(img, out, p, total, is_max ? 1 : 0, ctx.opts().ref_compat);
     return ctx.check_cuda(cudaGetLastError(), "pool2d launch");
 }
 

@@ -48,6 +48,10 @@ struct Window {
 };
 sage_status im2col(Context &ctx, const float *img, float *col, long long n, long long img_h, long long img_w,
                    long long chan, long long col_h, long long col_w, const Window &w);
+// im2col writing the fp32 column tensor (`col`, row pitch K, may be null) and / or its tf32 planes
+// (`hi`, lo `plane` floats further, row pitch `pitch` >= K and a multiple of 4, may be null).
+sage_status im2col_planes(Context &ctx, const float *img, long long n, long long img_h, long long img_w, long long chan,
+                          long long col_h, long long col_w, const Window &w, float *col, float *hi, long long plane, int pitch);
 sage_status col2im(Context &ctx, const float *col, float *img, long long n, long long img_h, long long img_w,
                    long long chan, long long col_h, long long col_w, const Window &w);
 sage_status pool2d(Context &ctx, bool is_max, const float *img, float *out, long long n, long long img_h,
