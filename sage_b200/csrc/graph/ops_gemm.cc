@@ -193,6 +193,10 @@ struct GemmOp : Operator {
         return {g(x[1], gy, true, true), g(gy, x[0], true, true)};
     }
 
+    // Implicit GEMM needs 32-channel K-blocks; images below 128 KiB take the explicit path (im2col-mode
+    // tensor maps over very small tensors are avoided).
+    bool conv_implicit() const { return conv && img[3] % 32 == 0 && img[0] * img[1] * img[2] * img[3] * 4 >= 131072; }
+
     void dims_from_inputs() {  // m, n, k, batch from in[0] / in[1] (last two axes = matrix)
         const Shape &a = in[0].shape, &b = in[1].shape;
         const int ra = a.rank(), rb = b.rank();
@@ -238,8 +242,24 @@ struct GemmOp : Operator {
         std::shared_ptr<SplitCache> hold_a, hold_b;
         bool sw_a = false, sw_b = false;
         Block *col_block = nullptr;  // conv: the column matrix exists only as tf32 planes, only for this launch
-        if (conv) {
-            if (!x[0].desc.shape.has_default_strides() || ta) return ctx.fail(SAGE_ERR_INVALID, "internal: conv gemm needs a contiguous image");
+        if (conv && (!x[0].desc.shape.has_default_strides() || ta)) return ctx.fail(SAGE_ERR_INVALID, "internal: conv gemm needs a contiguous image");
+        if (conv_implicit() && x[0].desc.shape.offset % 4 == 0) {
+            // implicit GEMM: im2col-mode TMA reads the image's tf32 planes, nothing is materialised
+            st = storage_planes(ctx, *x[0].data);
+            if (st) return st;
+            hold_a = x[0].data->split;
+            g.conv.on = true;
+            g.conv.hi = hold_a->planes.planes + x[0].desc.shape.offset;
+            g.conv.plane = hold_a->plane;
+            g.conv.n = img[0];
+            g.conv.h = img[1];
+            g.conv.w = img[2];
+            g.conv.c = img[3];
+            g.conv.out_h = img[4];
+            g.conv.out_w = img[5];
+            g.conv.win = win;
+        } else if (conv) {
+            if (x[0].data->planes_only) return ctx.fail(SAGE_ERR_INVALID, "internal: a planes-only image reached the explicit im2col path");
             const int pitch = (int)((k + 3) / 4 * 4);
             const long long plane = m * pitch;
             col_block = ctx.allocator().alloc((size_t)plane * 2 * sizeof(float));
@@ -525,7 +545,7 @@ bool is_grouped_gemm_op(const Operator &op);
 bool gemm_operand_static_direct(const Operator &op, int idx) {
     if (is_grouped_gemm_op(op)) return idx == 0 && gemm_operand_view_ok(op.in[0].shape);
     const GemmOp *g = as_gemm(op);
-    if (g && g->conv && idx == 0) return false;  // the image is read by im2col, as fp32
+    if (g && g->conv && idx == 0) return g->conv_implicit();  // implicit GEMM reads the image's planes; else im2col reads fp32
     return g && idx >= 0 && idx < 2 && gemm_operand_view_ok(g->in[idx].shape);
 }
 
@@ -533,7 +553,7 @@ std::string describe_gemm(const Operator &op) {
     const GemmOp *g = as_gemm(op);
     if (!g) return "";
     std::string s;
-    if (g->conv) s += "<im2col>";
+    if (g->conv) s += g->conv_implicit() ? "<implicit conv>" : "<im2col>";
     if (!g->epilogue.empty()) s += "{" + g->epilogue + "}";
     if (g->folded) s += "[store]";
     return s;

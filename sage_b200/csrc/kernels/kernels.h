@@ -107,7 +107,17 @@ struct TcAuxArg {
     long long s0 = 0, s1 = 0, sr = 0;
     int sc = 0;
 };
+// Implicit-GEMM convolution: A (one row per output pixel, K over (tap, channel)) is read by im2col-mode
+// TMA from the tf32 planes of a contiguous NHWC image; needs C % 32 == 0.
+struct TcConv {
+    bool on = false;
+    const float *hi = nullptr;  // hi plane of the image; lo `plane` floats further
+    long long plane = 0;
+    long long n = 0, h = 0, w = 0, c = 0, out_h = 0, out_w = 0;
+    Window win{};
+};
 struct TcGemm {
+    TcConv conv;             // when conv.on, `a` is ignored
     bool a_kmajor = true, b_kmajor = false;  // is K the contiguous axis of the operand as stored
     long long m = 0, n = 0, k = 0, batch = 1;
     TcOperand a, b;
