@@ -2,8 +2,10 @@
 //
 // Reference: Im2col::compute (src/ops/conv.rs:289-374) gives each (y, x, c) of the column grid to a
 // work-item that loops over the batch and the taps; Col2im::compute (:404-498) is the inverse
-// gather-sum.  Here one thread produces one output element with the channel innermost, so both the
-// image reads and the column writes coalesce.  pool2d evaluates max/avg pooling
+// gather-sum.  Here im2col gives a warp to each output pixel (see im2col_kernel) and can write the
+// tf32 hi / lo planes of the column matrix for the tensor-core GEMM in the same pass; convolutions
+// whose channel count is a multiple of 32 do not come here at all (the GEMM loads image tiles with
+// im2col-mode TMA).  pool2d evaluates max/avg pooling
 // (conv.rs:143-165: im2col, then a reduction over [KH,KW]) straight from the image without
 // materialising the KH*KW-times larger column tensor.  Padded taps count as zeros, and with
 // ref_compat the max starts from 0 like the reference's reduce accumulator.
