@@ -159,6 +159,9 @@ sage_status map_plan(const std::string &expr, const std::vector<MapOperand> &in,
     s << "extern \"C\" __global__ void __launch_bounds__(256) sage_map(";
     for (int q = 0; q < nin; ++q) s << "const " << ctype(in[q].dtype) << " *__restrict__ x" << q << "_buf, ";
     s << ctype(out_dtype) << " *__restrict__ y, const MapP p) {\n";
+    // launched as a programmatic dependent: wait for the kernel before this one before touching memory
+    s << "  asm volatile(\"griddepcontrol.launch_dependents;\" ::: \"memory\");\n";
+    s << "  asm volatile(\"griddepcontrol.wait;\" ::: \"memory\");\n";
     s << "  const " << it << " q = (" << it << ")blockIdx.x * blockDim.x + threadIdx.x;\n";
     s << "  const " << it << " g = q * " << vec << ";\n";
     s << "  if (g >= (" << it << ")p.n) return;\n";
@@ -270,7 +273,7 @@ sage_status map_launch(Context &ctx, const std::string &expr, const std::vector<
         for (char &ch : label)
             if (ch == ' ') ch = '_';
     }
-    return ctx.launch(mod, "sage_map", grid, block, 0, params.data(), label.empty() ? nullptr : label.c_str());
+    return ctx.launch(mod, "sage_map", grid, block, 0, params.data(), label.empty() ? nullptr : label.c_str(), true);
 }
 
 }  // namespace sage

@@ -16,6 +16,7 @@
 #include <cuda_runtime.h>
 
 #include "kernels.h"
+#include "launch.h"
 #include "gemm_tc_device.inc"  // split_tf32_value
 
 namespace sage {
@@ -71,6 +72,7 @@ __device__ __forceinline__ void row_store1(const RowParams &p, long long at, flo
 // V = float4 chunks per lane; the row has cols/4 <= 32*V chunks.
 template <int MODE, int V>
 __global__ void __launch_bounds__(256) row_warp_kernel(RowParams p) {
+    grid_dependency_sync();
     const int lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= p.rows) return;
@@ -164,6 +166,7 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float *smem)
 // registers (V float4 chunks per thread), so HBM still sees one read and one write per element.
 template <int MODE, int V>
 __global__ void __launch_bounds__(256) row_cta_kernel(RowParams p) {
+    grid_dependency_sync();
     __shared__ float smem[8];
     const long long row = blockIdx.x;
     const int chunks = (int)(p.cols >> 2);
@@ -236,6 +239,7 @@ __global__ void __launch_bounds__(256) row_cta_kernel(RowParams p) {
 // Any row length: one CTA per row, the row is re-read per pass.
 template <int MODE>
 __global__ void __launch_bounds__(256) row_block_kernel(RowParams p) {
+    grid_dependency_sync();
     __shared__ float smem[8];
     const long long row = blockIdx.x;
     const float *xr = p.x + row * p.cols;
@@ -276,6 +280,7 @@ static sage_status launch_rows(Context &ctx, RowParams p, const char *name) {
     ctx.note_launch(name);
     if (ctx.dry() || p.rows == 0) return SAGE_OK;
     p.ref_compat = ctx.opts().ref_compat;
+    cudaError_t err = cudaSuccess;
     const bool aligned = (reinterpret_cast<uintptr_t>(p.x) % 16 == 0) &&
                          (MODE == ROW_LSE || reinterpret_cast<uintptr_t>(p.y) % 16 == 0) &&
                          (!p.hi || (reinterpret_cast<uintptr_t>(p.hi) % 16 == 0 && p.plane % 4 == 0));
@@ -284,22 +289,22 @@ static sage_status launch_rows(Context &ctx, RowParams p, const char *name) {
         const int v = (chunks + 31) / 32;
         const unsigned blocks = (unsigned)((p.rows + 7) / 8);
         cudaStream_t s = ctx.stream();
-        if (v <= 1) row_warp_kernel<MODE, 1><<<blocks, 256, 0, s>>>(p);
-        else if (v <= 2) row_warp_kernel<MODE, 2><<<blocks, 256, 0, s>>>(p);
-        else if (v <= 4) row_warp_kernel<MODE, 4><<<blocks, 256, 0, s>>>(p);
-        else if (v <= 8) row_warp_kernel<MODE, 8><<<blocks, 256, 0, s>>>(p);
-        else row_warp_kernel<MODE, 16><<<blocks, 256, 0, s>>>(p);
+        if (v <= 1) err = launch_dependent(ctx.pdl, s, row_warp_kernel<MODE, 1>, dim3(blocks), dim3(256), 0, p);
+        else if (v <= 2) err = launch_dependent(ctx.pdl, s, row_warp_kernel<MODE, 2>, dim3(blocks), dim3(256), 0, p);
+        else if (v <= 4) err = launch_dependent(ctx.pdl, s, row_warp_kernel<MODE, 4>, dim3(blocks), dim3(256), 0, p);
+        else if (v <= 8) err = launch_dependent(ctx.pdl, s, row_warp_kernel<MODE, 8>, dim3(blocks), dim3(256), 0, p);
+        else err = launch_dependent(ctx.pdl, s, row_warp_kernel<MODE, 16>, dim3(blocks), dim3(256), 0, p);
     } else if (p.cols % 4 == 0 && p.cols <= 16384 && aligned && p.rows < (1LL << 31)) {
         const int v = (int)((p.cols / 4 + 255) / 256);
         const unsigned blocks = (unsigned)p.rows;
         cudaStream_t s = ctx.stream();
-        if (v <= 4) row_cta_kernel<MODE, 4><<<blocks, 256, 0, s>>>(p);
-        else if (v <= 8) row_cta_kernel<MODE, 8><<<blocks, 256, 0, s>>>(p);
-        else row_cta_kernel<MODE, 16><<<blocks, 256, 0, s>>>(p);
+        if (v <= 4) err = launch_dependent(ctx.pdl, s, row_cta_kernel<MODE, 4>, dim3(blocks), dim3(256), 0, p);
+        else if (v <= 8) err = launch_dependent(ctx.pdl, s, row_cta_kernel<MODE, 8>, dim3(blocks), dim3(256), 0, p);
+        else err = launch_dependent(ctx.pdl, s, row_cta_kernel<MODE, 16>, dim3(blocks), dim3(256), 0, p);
     } else {
-        row_block_kernel<MODE><<<(unsigned)p.rows, 256, 0, ctx.stream()>>>(p);
+        err = launch_dependent(ctx.pdl, ctx.stream(), row_block_kernel<MODE>, dim3((unsigned)p.rows), dim3(256), 0, p);
     }
-    return ctx.check_cuda(cudaGetLastError(), name);
+    return ctx.check_cuda(err, name);
 }
 
 sage_status softmax_rows(Context &ctx, const float *x, float *y, long long rows, long long cols, float *hi, long long plane) {

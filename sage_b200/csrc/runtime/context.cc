@@ -2,6 +2,7 @@
 // Reference counterparts: Device::new (src/session/device.rs:45-71), Context::with_device
 // (src/session/context.rs:43-52), KernelProgram::new (device.rs:201-213),
 // Context::get_program_with_id (context.rs:62-83), Kernel::launch (device.rs:297-318).
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 #include <nvrtc.h>
@@ -24,6 +25,7 @@ typedef int (*PFN_cuModuleGetFunction)(CUfunc_st **, CUmod_st *, const char *);
 typedef int (*PFN_cuLaunchKernel)(CUfunc_st *, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
                                   cudaStream_t, void **, void **);
 typedef int (*PFN_cuFuncSetAttribute)(CUfunc_st *, int, int);
+typedef CUresult (*PFN_cuLaunchKernelEx)(const CUlaunchConfig *, CUfunction, void **, void **);
 typedef int (*PFN_cuGetErrorString)(int, const char **);
 
 struct Driver {
@@ -32,6 +34,7 @@ struct Driver {
     PFN_cuModuleUnload ModuleUnload = nullptr;
     PFN_cuModuleGetFunction ModuleGetFunction = nullptr;
     PFN_cuLaunchKernel LaunchKernel = nullptr;
+    PFN_cuLaunchKernelEx LaunchKernelEx = nullptr;
     PFN_cuFuncSetAttribute FuncSetAttribute = nullptr;
     PFN_cuGetErrorString GetErrorString = nullptr;
     bool ok = false;
@@ -46,6 +49,7 @@ static Driver &driver() {
             d.ModuleUnload = (PFN_cuModuleUnload)dlsym(d.lib, "cuModuleUnload");
             d.ModuleGetFunction = (PFN_cuModuleGetFunction)dlsym(d.lib, "cuModuleGetFunction");
             d.LaunchKernel = (PFN_cuLaunchKernel)dlsym(d.lib, "cuLaunchKernel");
+            d.LaunchKernelEx = (PFN_cuLaunchKernelEx)dlsym(d.lib, "cuLaunchKernelEx");
             d.FuncSetAttribute = (PFN_cuFuncSetAttribute)dlsym(d.lib, "cuFuncSetAttribute");
             d.GetErrorString = (PFN_cuGetErrorString)dlsym(d.lib, "cuGetErrorString");
             d.ok = d.ModuleLoadData && d.ModuleGetFunction && d.LaunchKernel;
@@ -102,6 +106,7 @@ sage_status Context::create(int device, const sage_ctx_opts &opts, Context **out
     if (const char *e = getenv("SAGE_PATTERN_FUSION")) c->opts_.pattern_fusion = atoi(e);
     if (const char *e = getenv("SAGE_GEMM_BACKEND")) c->opts_.gemm_backend = atoi(e);
     if (const char *e = getenv("SAGE_VERBOSE_NAMES")) c->verbose_names = atoi(e) != 0;
+    if (const char *e = getenv("SAGE_PDL")) c->pdl = atoi(e) != 0;
     uint64_t cap = opts.mem_capacity_bytes;
     if (const char *e = getenv("SAGE_MEM_CAP")) cap = strtoull(e, nullptr, 10);
     if (device < 0) {
@@ -222,7 +227,7 @@ sage_status Context::module_get(const std::string &src, Module **out) {
 }
 
 sage_status Context::launch(Module *m, const char *name, const uint32_t grid[3], const uint32_t block[3],
-                            uint32_t smem, void **params, const char *label) {
+                            uint32_t smem, void **params, const char *label, bool dependent) {
     note_launch(label && verbose_names ? label : name);
     if (dry()) return SAGE_OK;
     Driver &d = driver();
@@ -237,7 +242,28 @@ sage_status Context::launch(Module *m, const char *name, const uint32_t grid[3],
         fn = it->second;
     }
     if (grid[0] == 0 || grid[1] == 0 || grid[2] == 0) return SAGE_OK;
-    int e = d.LaunchKernel(fn, grid[0], grid[1], grid[2], block[0], block[1], block[2], smem, stream_, params, nullptr);
+    int e;
+    if (dependent && pdl && d.LaunchKernelEx) {
+        CUlaunchAttribute attr;
+        memset(&attr, 0, sizeof attr);
+        attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+        attr.value.programmaticStreamSerializationAllowed = 1;
+        CUlaunchConfig cfg;
+        memset(&cfg, 0, sizeof cfg);
+        cfg.gridDimX = grid[0];
+        cfg.gridDimY = grid[1];
+        cfg.gridDimZ = grid[2];
+        cfg.blockDimX = block[0];
+        cfg.blockDimY = block[1];
+        cfg.blockDimZ = block[2];
+        cfg.sharedMemBytes = smem;
+        cfg.hStream = stream_;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        e = d.LaunchKernelEx(&cfg, fn, params, nullptr);
+    } else {
+        e = d.LaunchKernel(fn, grid[0], grid[1], grid[2], block[0], block[1], block[2], smem, stream_, params, nullptr);
+    }
     if (e) return fail(SAGE_ERR_DEVICE, std::string("cuLaunchKernel(") + name + "): " + cu_err(e));
     return SAGE_OK;
 }

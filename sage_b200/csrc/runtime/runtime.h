@@ -114,8 +114,13 @@ public:
     sage_status check_cuda(int err, const char *what);
 
     sage_status module_get(const std::string &src, Module **out);
+    // `dependent`: the kernel begins with griddepcontrol.wait, so it may be launched with programmatic
+    // stream serialisation (its prologue overlaps the tail of the kernel before it).
     sage_status launch(Module *m, const char *name, const uint32_t grid[3], const uint32_t block[3],
-                       uint32_t smem, void **params, const char *label = nullptr);
+                       uint32_t smem, void **params, const char *label = nullptr, bool dependent = false);
+    // Programmatic dependent launch for the library's own kernels that wait on the grid dependency
+    // themselves (GEMM, row kernels, generated maps).  Off with SAGE_PDL=0.
+    bool pdl = true;
     // When set, JIT-compiled map kernels are recorded under "map{<expression>}" instead of
     // "sage_map" in traces and profiles (more names, same launches).
     bool verbose_names = false;
