@@ -95,6 +95,11 @@ const char *sage_last_error(sage_ctx *ctx);
 /* Device-side status word: kernels with bounded waits set bits here instead of trapping.
  * Reads (and clears) it after synchronising the stream. */
 sage_status sage_status_word(sage_ctx *ctx, uint32_t *word);
+/* Self-test of the bounded waits (no counterpart in the reference, whose kernels never wait on one
+ * another): enqueues a kernel that waits, with the tensor-core GEMM's own bounded wait, on a
+ * barrier nothing arrives on.  The wait gives up after its limit (about one second), the kernel
+ * sets bits 0x140 in the status word and returns normally; the context stays usable. */
+sage_status sage_selftest_bounded_wait(sage_ctx *ctx);
 /* The context's CUDA stream as an opaque cudaStream_t (for event timing by the caller). */
 void *sage_ctx_stream(sage_ctx *ctx);
 

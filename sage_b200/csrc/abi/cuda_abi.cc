@@ -109,6 +109,11 @@ sage_status sage_status_word(sage_ctx *ctx, uint32_t *word) {
     return SAGE_OK;
 }
 
+sage_status sage_selftest_bounded_wait(sage_ctx *ctx) {
+    CTX_OR_FAIL(ctx);
+    return k::bounded_wait_selftest(C);
+}
+
 void *sage_ctx_stream(sage_ctx *ctx) { return (ctx && ctx->impl) ? (void *)ctx->impl->stream() : nullptr; }
 
 // ---------------------------------------------------------------- memory

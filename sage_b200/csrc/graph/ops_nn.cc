@@ -55,6 +55,14 @@ struct RowOp : Operator {
     }
 };
 
+bool row_op_is_softmax(const Operator &op, long long *rows, long long *cols) {
+    const RowOp *r = dynamic_cast<const RowOp *>(&op);
+    if (!r || r->kind != RSoftmax) return false;
+    *rows = r->rows;
+    *cols = r->cols;
+    return true;
+}
+
 bool row_op_emits_planes(const Operator &op) {
     const RowOp *r = dynamic_cast<const RowOp *>(&op);
     return r && r->kind != RLse;

@@ -43,6 +43,8 @@ std::shared_ptr<Operator> gemm_with_epilogue(const Operator &op, const std::stri
 std::shared_ptr<Operator> gemm_with_im2col(const Operator &op, const Operator &im2col_op, bool tc_enabled);
 std::shared_ptr<Operator> gemm_with_store(const Operator &op, const Shape &view, const TensorDesc &out, bool tc_enabled);
 bool row_op_emits_planes(const Operator &op);
+bool row_op_is_softmax(const Operator &op, long long *rows, long long *cols);
+std::shared_ptr<Operator> gemm_with_row_softmax(const Operator &op, long long rows, long long cols, const TensorDesc &out, bool tc_enabled);
 bool is_grouped_gemm_op(const Operator &op);
 bool gemm_operand_static_direct(const Operator &op, int idx);
 bool gemm_group_key(const Operator &op, std::string *key);
@@ -136,9 +138,9 @@ static bool reshape_keeps_matrix(const Operator &op) {
     return ra >= 2 && rb >= 2 && a[ra - 1] == b[rb - 1] && a[ra - 2] == b[rb - 2];
 }
 
-static void lower(Node &n, bool tc) {
+static void lower(Node &n, bool tc, bool softmax_in_gemm) {
     if (n.is_data) return;
-    for (Node &a : n.args) lower(a, tc);
+    for (Node &a : n.args) lower(a, tc, softmax_in_gemm);
     // operands behind an organize() copy
     if (is_gemm_op(*n.op) && gemm_runs_on_tc(*n.op, tc)) {
         {  // the column matrix of a convolution: made by the GEMM itself, as planes
@@ -162,6 +164,20 @@ static void lower(Node &n, bool tc) {
             Node inner = std::move(p->args[0]);
             n.args[idx] = std::move(inner);
             n.op = f;
+        }
+        return;
+    }
+    long long sm_rows, sm_cols;
+    if (softmax_in_gemm && row_op_is_softmax(*n.op, &sm_rows, &sm_cols) && n.args.size() == 1) {  // softmax over a product's rows
+        Node *p = &n.args[0];
+        while (!p->is_data && is_reshape_op(*p->op)) p = &p->args[0];
+        if (!p->is_data && is_gemm_op(*p->op)) {
+            std::shared_ptr<Operator> f = gemm_with_row_softmax(*p->op, sm_rows, sm_cols, n.op->out, tc);
+            if (f) {
+                std::vector<Node> args = std::move(p->args);
+                n.op = f;
+                n.args = std::move(args);
+            }
         }
         return;
     }
@@ -302,7 +318,7 @@ static void mark_plane_readers(Node &n, bool tc, std::unordered_set<Origin *> *s
 }
 
 // Program::compile, session.rs:62-206.
-static std::unique_ptr<Program> compile(const std::vector<Var> &x, std::vector<Var> y, bool fusion, bool pattern, bool tc) {
+static std::unique_ptr<Program> compile(const std::vector<Var> &x, std::vector<Var> y, bool fusion, bool pattern, bool tc, bool softmax_in_gemm) {
     std::unique_ptr<Program> p(new Program());
     p->fusion = fusion;
     p->pattern = pattern;
@@ -382,7 +398,7 @@ static std::unique_ptr<Program> compile(const std::vector<Var> &x, std::vector<V
         }
         r.root = build(node, in_keys, fusion, pattern, true);
         if (pattern) {
-            lower(r.root, tc);
+            lower(r.root, tc, softmax_in_gemm);
             if (tc) group_gemms(r.root);
         }
         p->routines.emplace(node.key(), std::move(r));
@@ -554,7 +570,7 @@ sage_status Session::eval(const std::vector<Var> &targets) {
     if (!prog) {
         std::unique_ptr<Program> p;
         try {
-            p = compile(x, y, true, ctx_->opts().pattern_fusion != 0, ctx_->opts().gemm_backend != 1);
+            p = compile(x, y, true, ctx_->opts().pattern_fusion != 0, ctx_->opts().gemm_backend != 1, (ctx_->opts().pattern_fusion & 2) != 0);
         } catch (const ShapeError &e) {
             return ctx_->fail(SAGE_ERR_INVALID, e.msg);
         }

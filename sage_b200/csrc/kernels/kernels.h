@@ -128,6 +128,7 @@ struct TcGemm {
     int naux = 0;
     TcAuxArg aux[3];
     std::string epilogue;    // C expression over x0 (the product) and x1..x3 (aux); empty = x0
+    bool row_softmax = false;  // store softmax over each output row of the expression; needs n <= 256 (one tile per row)
 };
 bool gemm_tc_shape_ok(long long m, long long n, long long k, long long batch);
 sage_status gemm_tc_run(Context &ctx, const TcGemm &g);
@@ -139,6 +140,8 @@ struct SplitView {
     long long sb1 = 0, sb0 = 0, ld = 0, col_stride = 1;
 };
 sage_status split_tf32_view(Context &ctx, const float *src, const SplitView &v, SplitPlanes *out);
+// Launches a kernel whose bounded wait runs out (nothing arrives on its barrier): ~1 s, then status bit 0x140.
+sage_status bounded_wait_selftest(Context &ctx);
 sage_status gemm_simt(Context &ctx, const GemmArgs &g);
 // Returns SAGE_ERR_UNSUPPORTED when the shape/alignment cannot go through TMA; the caller
 // then uses gemm_simt.

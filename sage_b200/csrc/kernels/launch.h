@@ -19,19 +19,36 @@ __device__ __forceinline__ void grid_dependency_sync() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// `cluster` > 1 launches thread-block clusters of that many CTAs along x (the grid must be a multiple).
 template <typename... P, typename... A>
-inline cudaError_t launch_dependent(bool pdl, cudaStream_t stream, void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, A &&...args) {
+inline cudaError_t launch_dependent(bool pdl, cudaStream_t stream, int cluster, void (*kernel)(P...), dim3 grid, dim3 block, size_t smem,
+                                    A &&...args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    unsigned n = 0;
+    if (pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = (unsigned)cluster;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
+    cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<A>(args)...);
+}
+template <typename... P, typename... A>
+inline cudaError_t launch_dependent(bool pdl, cudaStream_t stream, void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, A &&...args) {
+    return launch_dependent(pdl, stream, 1, kernel, grid, block, smem, std::forward<A>(args)...);
 }
 
 }  // namespace k

@@ -227,7 +227,7 @@ sage_status Context::module_get(const std::string &src, Module **out) {
 }
 
 sage_status Context::launch(Module *m, const char *name, const uint32_t grid[3], const uint32_t block[3],
-                            uint32_t smem, void **params, const char *label, bool dependent) {
+                            uint32_t smem, void **params, const char *label, bool dependent, int cluster) {
     note_launch(label && verbose_names ? label : name);
     if (dry()) return SAGE_OK;
     Driver &d = driver();
@@ -243,11 +243,23 @@ sage_status Context::launch(Module *m, const char *name, const uint32_t grid[3],
     }
     if (grid[0] == 0 || grid[1] == 0 || grid[2] == 0) return SAGE_OK;
     int e;
-    if (dependent && pdl && d.LaunchKernelEx) {
-        CUlaunchAttribute attr;
-        memset(&attr, 0, sizeof attr);
-        attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
-        attr.value.programmaticStreamSerializationAllowed = 1;
+    if (cluster > 1 && !d.LaunchKernelEx) return fail(SAGE_ERR_DEVICE, "cuLaunchKernelEx is not available for a cluster launch");
+    if (((dependent && pdl) || cluster > 1) && d.LaunchKernelEx) {
+        CUlaunchAttribute attr[2];
+        memset(attr, 0, sizeof attr);
+        unsigned nattr = 0;
+        if (dependent && pdl) {
+            attr[nattr].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+            attr[nattr].value.programmaticStreamSerializationAllowed = 1;
+            ++nattr;
+        }
+        if (cluster > 1) {
+            attr[nattr].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+            attr[nattr].value.clusterDim.x = (unsigned)cluster;
+            attr[nattr].value.clusterDim.y = 1;
+            attr[nattr].value.clusterDim.z = 1;
+            ++nattr;
+        }
         CUlaunchConfig cfg;
         memset(&cfg, 0, sizeof cfg);
         cfg.gridDimX = grid[0];
@@ -258,8 +270,8 @@ sage_status Context::launch(Module *m, const char *name, const uint32_t grid[3],
         cfg.blockDimZ = block[2];
         cfg.sharedMemBytes = smem;
         cfg.hStream = stream_;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = nattr;
         e = d.LaunchKernelEx(&cfg, fn, params, nullptr);
     } else {
         e = d.LaunchKernel(fn, grid[0], grid[1], grid[2], block[0], block[1], block[2], smem, stream_, params, nullptr);

@@ -117,7 +117,7 @@ public:
     // `dependent`: the kernel begins with griddepcontrol.wait, so it may be launched with programmatic
     // stream serialisation (its prologue overlaps the tail of the kernel before it).
     sage_status launch(Module *m, const char *name, const uint32_t grid[3], const uint32_t block[3],
-                       uint32_t smem, void **params, const char *label = nullptr, bool dependent = false);
+                       uint32_t smem, void **params, const char *label = nullptr, bool dependent = false, int cluster = 1);
     // Programmatic dependent launch for the library's own kernels that wait on the grid dependency
     // themselves (GEMM, row kernels, generated maps).  Off with SAGE_PDL=0.
     bool pdl = true;

@@ -191,7 +191,7 @@ def test_planes_only_intermediates():
         t, _ = attention_block(ctx, a, 4)
         ctx.eval(t["out"])
         d = ctx.describe()
-        assert d.count("=planes") >= 4 and "softmax=planes" in d
+        assert d.count("=planes") >= 4 and "softmax=planes" in d    # the probabilities exist only as tf32 planes
         got = ctx.read(t["out"])
         assert gemm_err(got, ref["out"]) <= 1e-4
         t2, _ = attention_block(ctx2, a, 4)
@@ -248,6 +248,51 @@ def test_implicit_gemm_convolution(shape, filt, stride, pad, dil):
         assert outs[0].shape == ref.shape
         assert gemm_err(outs[0], ref) <= 1e-4 and gemm_err(outs[1], ref) <= 1e-4
         assert gemm_err(outs[0], outs[1]) <= 1e-5
+        assert lowered.status_word() == 0
+    finally:
+        lowered.close()
+        plain.close()
+
+
+@pytest.mark.parametrize("b,lq,lk,d", [(6, 128, 128, 64), (5, 70, 96, 32), (3, 300, 200, 64), (4, 64, 256, 32), (2, 130, 33, 64)])
+def test_row_softmax_in_the_gemm_epilogue(b, lq, lk, d):
+    """softmax(q k^T * scale + mask) with the keys of a row inside one tile (L_k <= 256) can be computed by
+    the scores GEMM's epilogue warps (pattern_fusion bit 1; off by default because it measured slower on
+    the BERT step).  Ragged extents exercise partial tiles in both directions; the mask has
+    padded keys (-1e5) like the attention of config 4."""
+    rng = np.random.default_rng(b * 100 + lk)
+    q = rng.standard_normal((b, lq, d)).astype(np.float32)
+    k = rng.standard_normal((b, lk, d)).astype(np.float32)
+    v = rng.standard_normal((b, lk, d)).astype(np.float32)
+    mask = np.zeros((b, 1, lk), np.float32)
+    for i in range(b):
+        mask[i, 0, lk - int(rng.integers(0, lk // 3 + 1)):] = -100000.0
+    scale = np.float32(1.0 / np.sqrt(d))
+    s64 = q.astype(np.float64) @ k.astype(np.float64).transpose(0, 2, 1) * np.float64(scale) + mask
+    p64 = softmax64(s64)
+    o64 = p64 @ v.astype(np.float64)
+    lowered, plain = S.Context(0, pattern_fusion=3), S.Context(0, pattern_fusion=0)
+    try:
+        res = []
+        for ctx in (lowered, plain):
+            Q, K, V, M = (ctx.var(t) for t in (q, k, v, mask))
+            P = S.softmax(Q.matmul_batched(K.transpose(-1, -2)) * float(scale) + M, [-1])
+            O = P.matmul_batched(V)
+            ctx.trace_begin()
+            ctx.eval(P, O) if ctx is plain else ctx.eval(O)
+            res.append((ctx.read(O), ctx.trace()))
+        assert "|softmax" in lowered.describe() and "softmax_rows" not in res[0][1]
+        if lk % 4 == 0:  # the probabilities feed P.V as planes; an unaligned row pitch goes through the gather path
+            assert "|softmax=planes" in lowered.describe()
+        assert gemm_err(res[0][0], o64) <= 1e-4 and gemm_err(res[1][0], o64) <= 1e-4
+        assert gemm_err(res[0][0], res[1][0]) <= 1e-5
+        # the probabilities themselves, as a target
+        ctx = lowered
+        Q, K, M = (ctx.var(t) for t in (q, k, mask))
+        P = S.softmax(Q.matmul_batched(K.transpose(-1, -2)) * float(scale) + M, [-1])
+        got = P.eval(ctx)
+        assert "|softmax" in ctx.describe()
+        assert np.abs(got - p64).max() <= 1e-6 and np.abs(got.sum(-1) - 1).max() <= 1e-5
         assert lowered.status_word() == 0
     finally:
         lowered.close()

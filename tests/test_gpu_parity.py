@@ -469,6 +469,27 @@ def test_resnet18_vs_oracle(ctx):
 
 
 # ------------------------------------------------------------------------------ runtime behaviour
+def test_bounded_wait_runs_out_and_reports():
+    """Every device-side wait has a limit.  The self-test kernel waits on a barrier nothing arrives on:
+    after about a second the wait gives up, the kernel returns, the status word says so, and the
+    context goes on working (no trap, no hang, no fault)."""
+    import time
+    c = S.Context(0)
+    try:
+        assert c.status_word() == 0
+        t0 = time.perf_counter()
+        c._ck(S.lib.sage_selftest_bounded_wait(c.h))
+        assert c.status_word() == 0x140              # reading synchronises and clears the word
+        assert 0.2 < time.perf_counter() - t0 < 10.0
+        a = np.random.default_rng(1).uniform(-1, 1, (256, 256)).astype(np.float32)
+        got = S.matmul(c.var(a), c.var(a)).eval(c)   # the context is still good
+        assert gemm_err(got, a.astype(np.float64) @ a.astype(np.float64)) <= 1e-4
+        assert c.status_word() == 0
+    finally:
+        c.close()
+
+
+
 def test_program_cache_and_allocator_reuse(ctx):
     x = ctx.var(np.ones((256, 256), np.float32))
     y = S.softmax(x * 2.0 + 1.0, [1])

@@ -242,6 +242,15 @@ def test_bert_base_plan():
     assert d.count("gemm{(((float)((x0 + x1) > sg_lit(0x00000000u))) * (x0 + x1))}=planes") == 12  # FFN up: bias + relu
     assert d.count("gemm{((x0 + x1) + x2)}") == 24                           # output / FFN down: bias + residual
     assert d.count("softmax=planes") == 12 and d.count("layer_norm+planes") == 24  # layer norm also feeds the residual
+    # pattern_fusion bit 1: the softmax moves into the scores GEMM's epilogue (L = 128 keys fit one tile)
+    c3 = S.Context(-1, pattern_fusion=3)
+    m3 = S.Bert(num_layers=1)
+    for p in m3.params():
+        c3.set(p, np.zeros(p.extents, np.float32))
+    c3.trace_begin()
+    c3.eval(m3.pass_(c3.var(np.zeros((32, 128), np.uint32)), c3.var(np.ones((32, 128), np.float32))))
+    assert "softmax_rows" not in c3.trace() and "|softmax=planes" in c3.describe()
+    c3.close()
     assert c.mem_stats()["mem_peak"] < 3 << 30
     c.close()
 
