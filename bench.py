@@ -46,8 +46,8 @@ def gemm_flops(batch, seq, c=CFG):
 
 
 # DRAM traffic of the dominant kernel per launch, from the ncu capture summarised in
-# profiles/bench_bert_base_gemm_traffic.md (5530 MB over the 72 tensor-core GEMM launches of one step).
-GEMM_DRAM_BYTES_PER_LAUNCH = 76.81e6
+# profiles/bench_bert_base_gemm_traffic.md (5800 MB over the 72 tensor-core GEMM launches of one step).
+GEMM_DRAM_BYTES_PER_LAUNCH = 80.56e6
 
 
 def tf32_library_peak(device):
