@@ -95,7 +95,9 @@ def extract(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: extract_reference_vectors.py <path to a checkout of ingim/sage>")
+    ref_root = sys.argv[1]
     data = extract(ref_root)
     out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.json")
     with open(out, "w") as f:
