@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include "kernels.h"
+#include "launch.h"
 
 namespace sage {
 namespace k {
@@ -21,6 +22,7 @@ struct IDims {
 // y[g] = x[ sum_{i != axis} c_i * x_str[i] + ind[...] * x_str[axis] ],  c = unravel(g, ind extents)
 __global__ void __launch_bounds__(256) gather_kernel(const uint32_t *__restrict__ x, const uint32_t *__restrict__ ind,
                                                      uint32_t *__restrict__ y, IDims d, int axis, long long n) {
+    grid_dependency_sync();
     for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < n; g += (long long)gridDim.x * blockDim.x) {
         long long rem = g, ind_idx = 0, x_idx = 0;
 #pragma unroll 1
@@ -41,6 +43,7 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint32_t *__restrict_
 // mathematically expected sum when indices repeat.
 __global__ void __launch_bounds__(256) scatter_kernel(const float *__restrict__ x, const uint32_t *__restrict__ ind,
                                                       float *__restrict__ y, IDims d, IDims xs, int axis, long long n) {
+    grid_dependency_sync();
     for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < n; g += (long long)gridDim.x * blockDim.x) {
         long long rem = g, ind_idx = 0, x_idx = 0, y_idx = 0;
 #pragma unroll 1
@@ -58,6 +61,7 @@ __global__ void __launch_bounds__(256) scatter_kernel(const float *__restrict__ 
 
 __global__ void __launch_bounds__(256) strided_copy_kernel(const uint32_t *__restrict__ x, uint32_t *__restrict__ y,
                                                            IDims d, long long n) {
+    grid_dependency_sync();
     for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < n; g += (long long)gridDim.x * blockDim.x) {
         long long rem = g, xi = 0, yi = 0;
 #pragma unroll 1
@@ -89,7 +93,7 @@ sage_status gather(Context &ctx, const uint32_t *x, const long long *x_str, cons
     long long n = ind_dims.size();
     ctx.note_launch("gather");
     if (ctx.dry() || n == 0) return SAGE_OK;
-    gather_kernel<<<grid_for(ctx, n), 256, 0, ctx.stream()>>>(x, ind, y, d, axis, n);
+    launch_dependent(ctx.pdl, ctx.stream(), gather_kernel, dim3(grid_for(ctx, n)), dim3(256), 0, x, ind, y, d, axis, n);
     return ctx.check_cuda(cudaGetLastError(), "gather launch");
 }
 
@@ -106,7 +110,7 @@ sage_status scatter_add(Context &ctx, const float *x, const long long *x_str, co
     long long n = ind_dims.size();
     ctx.note_launch("scatter");
     if (ctx.dry() || n == 0) return SAGE_OK;
-    scatter_kernel<<<grid_for(ctx, n), 256, 0, ctx.stream()>>>(x, ind, y, d, xs, axis, n);
+    launch_dependent(ctx.pdl, ctx.stream(), scatter_kernel, dim3(grid_for(ctx, n)), dim3(256), 0, x, ind, y, d, xs, axis, n);
     return ctx.check_cuda(cudaGetLastError(), "scatter launch");
 }
 
@@ -121,7 +125,7 @@ sage_status strided_copy(Context &ctx, const uint32_t *x, const Dims &dims, uint
     long long n = dims.size();
     ctx.note_launch("strided_copy");
     if (ctx.dry() || n == 0) return SAGE_OK;
-    strided_copy_kernel<<<grid_for(ctx, n), 256, 0, ctx.stream()>>>(x, y, d, n);
+    launch_dependent(ctx.pdl, ctx.stream(), strided_copy_kernel, dim3(grid_for(ctx, n)), dim3(256), 0, x, y, d, n);
     return ctx.check_cuda(cudaGetLastError(), "strided_copy launch");
 }
 

@@ -14,6 +14,7 @@
 #include <cuda_runtime.h>
 
 #include "kernels.h"
+#include "launch.h"
 
 namespace sage {
 namespace k {
@@ -74,6 +75,7 @@ __device__ __forceinline__ T shfl_down_t(T v, int off) {
 template <typename T, int G>
 __global__ void __launch_bounds__(256) reduce_kernel(const T *__restrict__ x, T *__restrict__ y, RDims outer, RDims inner,
                                                      long long n_out, long long n_in, int kind, int ref_compat) {
+    grid_dependency_sync();
     __shared__ T smem[8];
     const int groups_per_block = blockDim.x / G;
     long long out = (long long)blockIdx.x * groups_per_block + threadIdx.x / G;
@@ -123,6 +125,7 @@ __global__ void __launch_bounds__(256) reduce_kernel(const T *__restrict__ x, T 
 template <typename T, int G>
 __global__ void __launch_bounds__(256) reduce_vec_kernel(const T *__restrict__ x, T *__restrict__ y, RDims outer, long long n_out,
                                                          long long n_in, int kind, int ref_compat) {
+    grid_dependency_sync();
     struct alignas(16) V4 {
         T v[4];
     };
@@ -241,17 +244,17 @@ static sage_status launch_reduce(Context &ctx, int kind, const T *x, const Dims 
         if (outer.ext[i] > 1 && outer.str[i] % 4 != 0) vec = false;
     if (vec) {
         if (G == 32)
-            reduce_vec_kernel<T, 32><<<(unsigned)blocks, threads, 0, ctx.stream()>>>(x, y, outer, n_out, n_in, kind, compat);
+            launch_dependent(ctx.pdl, ctx.stream(), reduce_vec_kernel<T, 32>, dim3((unsigned)blocks), dim3(threads), 0, x, y, outer, n_out, n_in, kind, compat);
         else
-            reduce_vec_kernel<T, 256><<<(unsigned)blocks, threads, 0, ctx.stream()>>>(x, y, outer, n_out, n_in, kind, compat);
+            launch_dependent(ctx.pdl, ctx.stream(), reduce_vec_kernel<T, 256>, dim3((unsigned)blocks), dim3(threads), 0, x, y, outer, n_out, n_in, kind, compat);
         return ctx.check_cuda(cudaGetLastError(), "reduce launch");
     }
     if (G == 1)
-        reduce_kernel<T, 1><<<(unsigned)blocks, threads, 0, ctx.stream()>>>(x, y, outer, inner, n_out, n_in, kind, compat);
+        launch_dependent(ctx.pdl, ctx.stream(), reduce_kernel<T, 1>, dim3((unsigned)blocks), dim3(threads), 0, x, y, outer, inner, n_out, n_in, kind, compat);
     else if (G == 32)
-        reduce_kernel<T, 32><<<(unsigned)blocks, threads, 0, ctx.stream()>>>(x, y, outer, inner, n_out, n_in, kind, compat);
+        launch_dependent(ctx.pdl, ctx.stream(), reduce_kernel<T, 32>, dim3((unsigned)blocks), dim3(threads), 0, x, y, outer, inner, n_out, n_in, kind, compat);
     else
-        reduce_kernel<T, 256><<<(unsigned)blocks, threads, 0, ctx.stream()>>>(x, y, outer, inner, n_out, n_in, kind, compat);
+        launch_dependent(ctx.pdl, ctx.stream(), reduce_kernel<T, 256>, dim3((unsigned)blocks), dim3(threads), 0, x, y, outer, inner, n_out, n_in, kind, compat);
     return ctx.check_cuda(cudaGetLastError(), "reduce launch");
 }
 
@@ -277,6 +280,7 @@ __device__ __forceinline__ bool better(bool is_max, float v, unsigned i, float b
 template <int G>
 __global__ void __launch_bounds__(256) reduce_arg_kernel(const float *__restrict__ x, unsigned *__restrict__ y, RDims outer,
                                                          long long n_out, long long n_in, long long stride, int is_max) {
+    grid_dependency_sync();
     long long out = (long long)blockIdx.x * (blockDim.x / G) + threadIdx.x / G;
     const int lane = threadIdx.x % G;
     if (out >= n_out) return;
@@ -329,9 +333,9 @@ sage_status reduce_arg(Context &ctx, bool is_max, const float *x, const Dims &ou
     ctx.note_launch(G == 1 ? "reduce_arg_g1" : "reduce_arg_g32");
     if (ctx.dry()) return SAGE_OK;
     if (G == 1)
-        reduce_arg_kernel<1><<<(unsigned)blocks, threads, 0, ctx.stream()>>>(x, y, outer, n_out, inner_ext, inner_str, is_max);
+        launch_dependent(ctx.pdl, ctx.stream(), reduce_arg_kernel<1>, dim3((unsigned)blocks), dim3(threads), 0, x, y, outer, n_out, inner_ext, inner_str, is_max);
     else
-        reduce_arg_kernel<32><<<(unsigned)blocks, threads, 0, ctx.stream()>>>(x, y, outer, n_out, inner_ext, inner_str, is_max);
+        launch_dependent(ctx.pdl, ctx.stream(), reduce_arg_kernel<32>, dim3((unsigned)blocks), dim3(threads), 0, x, y, outer, n_out, inner_ext, inner_str, is_max);
     return ctx.check_cuda(cudaGetLastError(), "reduce_arg launch");
 }
 
