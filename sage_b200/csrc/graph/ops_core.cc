@@ -74,6 +74,11 @@ bool is_expand_op(const Operator &op) {
     const ViewOp *v = dynamic_cast<const ViewOp *>(&op);
     return v && v->kind == VExpand;
 }
+// 0 reshape, 1 expand, 2 permute, 3 squeeze, 4 unsqueeze, 5 slice; -1 when `op` is no view
+int view_op_kind(const Operator &op) {
+    const ViewOp *v = dynamic_cast<const ViewOp *>(&op);
+    return v ? (int)v->kind : -1;
+}
 
 static Var make_view(ViewKind kind, const Var &x, const Shape &shape, std::function<void(ViewOp &)> fill = nullptr) {
     auto op = std::make_shared<ViewOp>();
@@ -223,6 +228,16 @@ Var ops::scatter(const Var &x, const Var &ind, long long axis, const Array &exte
     op->in = {x.desc, ind.desc};
     op->out = TensorDesc(e, x.dtype());
     return Var::from_op(op, {x, ind});
+}
+
+// The axis of a gather (`scatter` false) or scatter operator, -1 when `op` is neither.
+int index_op_axis(const Operator &op, bool scatter) {
+    if (scatter) {
+        const ScatterOp *s = dynamic_cast<const ScatterOp *>(&op);
+        return s ? s->axis : -1;
+    }
+    const GatherOp *g = dynamic_cast<const GatherOp *>(&op);
+    return g ? g->axis : -1;
 }
 
 // ---------------------------------------------------------------- concat (core.rs:836-935)

@@ -61,6 +61,14 @@ struct ReduceOp : Operator {
     }
 };
 
+bool reduce_op_info(const Operator &op, int *kind, std::vector<int> *axes) {
+    const ReduceOp *r = dynamic_cast<const ReduceOp *>(&op);
+    if (!r) return false;
+    *kind = (int)r->kind;
+    *axes = r->axes;
+    return true;
+}
+
 Var ops::reduce(const Var &x, const std::vector<long long> &axes_in, bool preserve, Red kind) {
     std::vector<int> axes = to_axes(axes_in, x.rank());
     auto op = std::make_shared<ReduceOp>();

@@ -1,0 +1,32 @@
+// Whole-row programs: a graph of maps, row reductions, gathers and scatters along the row, all over one
+// [R, C] space, evaluated by ONE generated kernel that keeps each row on chip.
+//
+// The reference runs such a graph (e.g. softmax_cross_entropy of a fused map and its gradient,
+// examples/basics.rs:28-36, src/ops/nn.rs:58-82) as one kernel per map chain / reduction / gather /
+// scatter, each reading and writing full [R, C] tensors (Program::compile, src/session.rs:62-206,
+// decides which values are materialised).  Here every value of the graph lives in registers for the
+// row being processed: a block loads the row of each input once, walks the graph in topological
+// order (block reductions where the graph reduces along the row), and writes only the requested
+// outputs.  DRAM traffic is the compulsory one: inputs once, outputs once.
+#pragma once
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "graph.h"
+
+namespace sage {
+
+struct RowProgram;
+
+// Null when the graph below `targets` (cut at `evaluated` and at data variables) is not a row program.
+std::shared_ptr<RowProgram> row_program_build(const std::vector<Var> &evaluated, const std::vector<Var> &targets);
+// Allocates the targets, launches the kernel, stores the results in `s.data`.
+sage_status row_program_exec(RowProgram &p, Context &ctx, Session &s);
+// Are the evaluated values the program was cut at still held by the session?
+bool row_program_ready(const RowProgram &p, const Session &s);
+std::string row_program_describe(const RowProgram &p);
+// The generated CUDA source (for tests).
+const std::string &row_program_source(const RowProgram &p);
+
+}  // namespace sage

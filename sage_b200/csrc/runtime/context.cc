@@ -226,6 +226,25 @@ sage_status Context::module_get(const std::string &src, Module **out) {
     return SAGE_OK;
 }
 
+int Context::blocks_per_sm(Module *m, const char *name, int block_threads, uint32_t smem) {
+    if (dry()) return 1;
+    Driver &d = driver();
+    typedef int (*PFN_occupancy)(int *, CUfunc_st *, int, size_t);
+    static PFN_occupancy occupancy = (PFN_occupancy)dlsym(d.lib, "cuOccupancyMaxActiveBlocksPerMultiprocessor");
+    CUfunc_st *fn = nullptr;
+    auto it = m->functions.find(name);
+    if (it == m->functions.end()) {
+        if (d.ModuleGetFunction(&fn, m->cu_module, name)) return 1;
+        if (smem > 48 * 1024 && d.FuncSetAttribute) d.FuncSetAttribute(fn, 8 /*MAX_DYNAMIC_SHARED_SIZE_BYTES*/, (int)smem);
+        m->functions[name] = fn;
+    } else {
+        fn = it->second;
+    }
+    int n = 0;
+    if (!occupancy || occupancy(&n, fn, block_threads, smem) || n < 1) return 1;
+    return n;
+}
+
 sage_status Context::launch(Module *m, const char *name, const uint32_t grid[3], const uint32_t block[3],
                             uint32_t smem, void **params, const char *label, bool dependent, int cluster) {
     note_launch(label && verbose_names ? label : name);

@@ -114,6 +114,8 @@ public:
     sage_status check_cuda(int err, const char *what);
 
     sage_status module_get(const std::string &src, Module **out);
+    // How many blocks of `block_threads` threads and `smem` dynamic bytes of this kernel fit on one SM (>= 1).
+    int blocks_per_sm(Module *m, const char *name, int block_threads, uint32_t smem);
     // `dependent`: the kernel begins with griddepcontrol.wait, so it may be launched with programmatic
     // stream serialisation (its prologue overlaps the tail of the kernel before it).
     sage_status launch(Module *m, const char *name, const uint32_t grid[3], const uint32_t block[3],

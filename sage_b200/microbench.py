@@ -6,6 +6,7 @@ row kernels and f32-equivalent TFLOP/s of the tensor-core GEMM, each as one JSON
   python -m sage_b200.microbench --case reduce|softmax|layernorm|lse --rows 16384 --cols 4096
   python -m sage_b200.microbench --case config1 --rows 16384 --cols 4096  # whole forward + grad graph
   python -m sage_b200.microbench --case all
+  python -m sage_b200.microbench --case train_resnet --batch 128             # examples/train.rs: one Adam step of ResNet-18
   python -m sage_b200.microbench --case tf32_peak                          # library TF32 GEMM: the tensor-pipe denominator
 
 Times are device times from CUDA events recorded on the context's stream in front of every launch
@@ -80,7 +81,7 @@ def row_case(ctx, a, kind):
     def go():
         ctx.clear()
         ctx.eval(out)
-    ms, prof = timed(ctx, go, a.reps, names)
+    ms, prof = timed(ctx, go, a.reps, [""])  # every kernel of the evaluation (one, whichever way it is lowered)
     hbm, _, src = peaks()
     gbs = bytes_ / (ms * 1e-3) / 1e9
     return {"case": kind, "rows": rows, "cols": cols, "us": 1e3 * ms, "algorithmic_bytes": bytes_, "gb_per_s": gbs, "peak_hbm_gb_per_s": hbm,
@@ -104,6 +105,55 @@ def case_config1(ctx, a):
     gbs = bytes_ / (ms * 1e-3) / 1e9
     return {"case": "config1_fwd_grad", "rows": rows, "cols": cols, "us": 1e3 * ms, "compulsory_bytes": bytes_, "gb_per_s": gbs,
             "peak_hbm_gb_per_s": hbm, "frac": gbs / hbm, "peak_source": src, "kernels": {k: v for k, v in prof.items()}}
+
+
+def case_train_resnet(ctx, a):
+    """The reference's training example (examples/train.rs): ResNet d18(1, 10) on 28 x 28 x 1 images, batch
+    128, Adam(1e-4).  One step = upload of the batch from pinned memory, evaluation of loss + accuracy +
+    all gradients (Program::exec), Optimizer::update, read-back of loss and accuracy, Context::data.clear().
+    Device time per step from events around the whole loop; the kernel table is from a separate profiled step."""
+    batch = a.batch if a.batch > 1 else 128
+    rng = np.random.default_rng(6001)
+    model = S.ResNet18(1, 10)
+    for p in model.params():
+        e = p.extents
+        ctx.set(p, (rng.standard_normal(e) * (np.sqrt(2.0 / (e[0] * e[1] * e[2])) if len(e) == 4 else 0.05)).astype(np.float32))
+    xin, lin = S.Var.empty([batch, 28, 28, 1]), S.Var.empty([batch, 1], S.U32)
+    logits = model.pass_(xin)
+    loss = S.softmax_cross_entropy(logits, lin).mean([0], False)
+    acc = S.accuracy(logits, lin)
+    grads = S.grad_param(loss, model)
+    opt = S.Adam(1e-4)
+    opt.init(ctx)
+    hx, hl = ctx.pinned((batch, 28, 28, 1), np.float32), ctx.pinned((batch, 1), np.uint32)
+    hx[...] = rng.standard_normal(hx.shape).astype(np.float32)
+    hl[...] = rng.integers(0, 10, hl.shape).astype(np.uint32)
+    targets = list(grads.values()) + [loss, acc]
+    last = {}
+
+    def step():
+        ctx.set(xin, None, pinned_ptr=hx.ctypes.data)
+        ctx.set(lin, None, pinned_ptr=hl.ctypes.data)
+        ctx.eval(*targets)
+        opt.update(grads, ctx)
+        last["loss"], last["acc"] = float(ctx.read(loss)[0]), float(ctx.read(acc)[0])
+        ctx.clear()
+    for _ in range(3):
+        step()
+    first_loss = last["loss"]
+    ctx.sync()
+    ctx.timer_start()
+    for _ in range(a.reps):
+        step()
+    ms = ctx.timer_stop() / a.reps
+    ctx.profile_begin()
+    step()
+    prof = ctx.profile_end()
+    total = sum(t for n, t in prof.values())
+    top = sorted(prof.items(), key=lambda kv: -kv[1][1])[:8]
+    return {"case": "train_resnet18_mnist_shape", "batch": batch, "ms_per_step": ms, "images_per_s": batch / (ms * 1e-3),
+            "launches_per_step": sum(n for n, t in prof.values()), "loss_after_3_steps": first_loss, "loss_now": last["loss"],
+            "kernel_ms": {k: [n, round(t, 4)] for k, (n, t) in top}, "profiled_step_ms": total}
 
 
 def case_tf32_peak(a):
@@ -159,6 +209,8 @@ def main():
             r = case_gemm(ctx, a)
         elif c == "config1":
             r = case_config1(ctx, a)
+        elif c == "train_resnet":
+            r = case_train_resnet(ctx, a)
         else:
             r = row_case(ctx, a, c)
         print(json.dumps(r), flush=True)

@@ -172,7 +172,8 @@ def test_broadcast_and_strided_views(ctx):
 # ------------------------------------------------------------------------------ reductions
 @pytest.mark.parametrize("shape,axes,preserve", [
     ((64, 1000), [1], True), ((64, 1000), [0], False), ((7, 9, 11, 5), [0, 2], False), ((7, 9, 11, 5), [3, 1], True),
-    ((3, 20000), [1], False), ((5000, 3), [0], False), ((2, 3, 4), [0, 1, 2], False), ((1, 1), [1], True)])
+    ((3, 20000), [1], False), ((5000, 3), [0], False), ((2, 3, 4), [0, 1, 2], False), ((1, 1), [1], True),
+    ((128, 7, 7, 64), [0, 1, 2], False), ((6272, 100), [0], True), ((40000, 33), [0], False), ((70, 512), [0], False)])
 @pytest.mark.parametrize("kind", ["sum", "max", "min", "prod"])
 def test_reduce_vs_oracle(ctx, shape, axes, preserve, kind):
     rng = np.random.default_rng(10)
@@ -286,6 +287,67 @@ def test_config1_forward_and_grad(ctx):
     ref_loss, ref_gx = [t.numpy() for t in R.evaluate([rloss, rgx])]
     assert rel_err(ctx.read(loss), ref_loss) <= 1e-4
     assert rel_err(ctx.read(gx), ref_gx, floor=1e-5) <= 1e-4
+
+
+def row_graph(M, x, y, idx, pick):
+    """A graph that stays inside one [R, C] row space: maps, all four reductions over axis 1 (both
+    `preserve` forms), a gather and a scatter along the row, integer and uint values, a broadcast scalar."""
+    n = x.extent(0)
+    z = x * y + M.abs_(x) * 0.5
+    hi, lo = M.max_(z, [1], True), M.min_(z, [1], False)
+    e = M.exp(z - hi)
+    soft = e / M.sum_(e, [1], True)
+    picked = M.gather(z, idx, 1)                                      # [R, 1]
+    onehot = M.scatter(picked * 2.0, pick, 1, [n, x.extent(1)])
+    count = M.sum_(M.float_(M.gt(z, M.scalar(0.0, [1]))), [1], True)  # uint -> float
+    small = M.prod(y * 0.01 + 1.0, [1], True)
+    full = soft * count + onehot - M.view(lo, [n, 1]) * M.float_(M.int_(z)) + small
+    row = M.sum_(full, [1], False) + M.view(picked, [n])
+    return full, row, hi
+
+
+@pytest.mark.parametrize("rows,cols", [(1024, 1024), (37, 301), (5, 130), (9, 4100), (3, 8192), (4, 10000), (2, 16384)])
+def test_row_program_vs_oracle_and_kernel_by_kernel(rows, cols):
+    rng = np.random.default_rng(1100 + cols)
+    x = rng.standard_normal((rows, cols), dtype=np.float32)
+    y = rng.standard_normal((rows, cols), dtype=np.float32)
+    idx = rng.integers(0, cols, (rows, 1)).astype(np.uint32)
+    pick = rng.integers(0, cols, (rows, 1)).astype(np.int32)
+    outs = []
+    for fusion in (1, 5):  # 1: whole-row program; 5: the same graph kernel by kernel
+        c = S.Context(0, pattern_fusion=fusion)
+        try:
+            targets = row_graph(S, c.var(x), c.var(y), c.var(idx), c.var(pick))
+            c.trace_begin()
+            c.eval(*targets)
+            assert (c.trace() == ["sage_row_program"]) == (fusion == 1)
+            outs.append([c.read(t) for t in targets])
+            assert c.status_word() == 0
+        finally:
+            c.close()
+    ref = [t.numpy() for t in R.evaluate(list(row_graph(R, RV(x), RV(y), RV(idx, R.UINT), RV(pick, R.INT))))]
+    for a, b, r in zip(outs[0], outs[1], ref):
+        assert a.shape == b.shape == r.shape
+        assert rel_err(a, b, floor=1e-4) <= 1e-4      # f32 rel <= 1e-4 between the two partitions into kernels
+        assert rel_err(a, r, floor=1e-4) <= 1e-4      # and against the oracle
+    assert np.array_equal(outs[0][2], outs[1][2])      # the row maxima are exact either way
+
+
+def test_row_program_reads_evaluated_states(ctx):
+    """Leaves of a row program may be values the session already holds."""
+    rng = np.random.default_rng(1200)
+    x = rng.standard_normal((64, 512), dtype=np.float32)
+    xv = ctx.var(x)
+    z = (xv * 2.0).exp()
+    ctx.eval(z)                                   # now a state of the session
+    out = (z / z.sum([1], True) + xv).max([1], False)
+    ctx.trace_begin()
+    got = out.eval(ctx)
+    assert ctx.trace() == ["sage_row_program"] and "(2 inputs -> 1 outputs)" in ctx.describe()
+    e = np.exp(2.0 * x.astype(np.float64))
+    ref = (e / e.sum(1, keepdims=True) + x).max(1)
+    assert rel_err(got, ref.astype(np.float32), floor=1e-4) <= 1e-4
+    ctx.clear()
 
 
 # ------------------------------------------------------------------------------ config 2: contractions

@@ -79,9 +79,11 @@ def test_matmul_shapes(ctx):
     assert S.max_pool_2d(ctx.var(np.zeros((2, 112, 112, 64), np.float32)), 3, 2, 1, 1).extents == (2, 56, 56, 64)
 
 
-def test_config1_program_matches_reference_fusion(ctx):
+def test_config1_program_matches_reference_fusion():
     """src/session.rs + src/ops.rs::fuse: z = x*y + x*3.14 is ONE variadic kernel with x bound twice and
-    the literal folded in; z is materialised (it has several consumers)."""
+    the literal folded in; z is materialised (it has several consumers).  pattern_fusion bit 2 keeps the
+    whole-row program off, so the reference's own partition into kernels shows."""
+    ctx = S.Context(-1, pattern_fusion=5)
     x = ctx.var(np.zeros((1024, 1024), np.float32))
     y = ctx.var(np.zeros((1024, 1024), np.float32))
     lab = ctx.var(np.zeros((1024, 1), np.uint32))
@@ -93,6 +95,7 @@ def test_config1_program_matches_reference_fusion(ctx):
     assert d[0] == "variadic{((x0 * x1) + (x2 * sg_lit(0x4048f5c3u)))}(data,data,data)"
     assert "log_sum_exp(state)" in d[-1] and "gather" in d[-1]
     assert ctx.trace() == ["sage_map", "lse_rows", "sage_map", "gather", "reduce_g1", "sage_map"]
+    ctx.close()
     # without pattern fusion the reference's own kernel sequence appears (max, exp, sum, log...)
     c2 = S.Context(-1, pattern_fusion=0)
     x2 = c2.var(np.zeros((64, 64), np.float32))
@@ -100,6 +103,35 @@ def test_config1_program_matches_reference_fusion(ctx):
     c2.eval(S.log_sum_exp(x2, [1]))
     assert [k.split("_g")[0] for k in c2.trace()] == ["reduce", "sage_map", "reduce", "sage_map"]
     c2.close()
+
+
+def test_config1_runs_as_one_row_program(ctx):
+    """The whole forward + gradient graph of config 1 (maps, row reductions, gather, scatter over one
+    [R, C] space) becomes ONE generated kernel; graphs that leave the row space are compiled the ordinary way."""
+    x = ctx.var(np.zeros((1024, 1024), np.float32))
+    y = ctx.var(np.zeros((1024, 1024), np.float32))
+    lab = ctx.var(np.zeros((1024, 1), np.uint32))
+    loss = S.softmax_cross_entropy(x * y + x * 3.14, lab)
+    gx = x.grad(loss)
+    ctx.trace_begin()
+    ctx.eval(loss, gx)
+    assert ctx.trace() == ["sage_row_program"]
+    d = ctx.describe()
+    assert d.startswith("row_program[1024x1024; 128 threads x 8]") and "(3 inputs -> 2 outputs)" in d
+    n = ctx.programs_compiled()
+    ctx.clear()
+    ctx.eval(loss, gx)
+    assert ctx.programs_compiled() == n
+    # a reduction across rows is not row-local: ordinary program
+    ctx.clear()
+    ctx.trace_begin()
+    ctx.eval(loss.mean(0))
+    assert "sage_row_program" not in ctx.trace()
+    # rows that do not fill the block exactly, scalar accesses (C % 4 != 0), int data
+    w = ctx.var(np.zeros((7, 301), np.float32))
+    ctx.trace_begin()
+    ctx.eval(S.softmax(w, [1]).int().float().sum([1], True) * w)
+    assert ctx.trace() == ["sage_row_program"] and "[7x301; 96 threads x 4]" in ctx.describe()
 
 
 def test_grad_graph_and_program_cache(ctx):
