@@ -116,6 +116,26 @@ sage_status sage_op_softmax_cross_entropy(const sage_var *x, const sage_var *lab
 sage_status sage_op_layer_norm(const sage_var *x, int32_t naxes, const int64_t *axes, const sage_var *gamma,
                                const sage_var *beta, float eps, sage_var **out);                                  /* :84-100 */
 
+/* ---- metric, src/ops/metric.rs:4-17: share of rows whose argmax(logits, 1) equals the label */
+sage_status sage_op_accuracy(const sage_var *logits, const sage_var *labels, sage_var **out);
+
+/* ---- optimizers, src/optim.rs.  One in-place launch updates every parameter (and the optimizer's
+ * moments); the arithmetic per element is the reference's, in the reference's order.
+ * Sgd::new(lr) — optim.rs:28-40; Adam::new(lr) — optim.rs:112-125 (beta1 0.9, beta2 0.999, eps 1e-08). */
+typedef struct sage_optimizer sage_optimizer;
+sage_status sage_sgd_create(float lr, sage_optimizer **out);
+sage_status sage_adam_create(float lr, sage_optimizer **out);
+/* The private fields of the reference's structs (optim.rs:14-26, 97-110); Sgd's momentum stays 0 (with
+ * any other value the reference's update panics, optim.rs:68-69, and this one returns SAGE_ERR_UNSUPPORTED). */
+sage_status sage_optimizer_set_weight_decay(sage_optimizer *o, float weight_decay);
+sage_status sage_optimizer_destroy(sage_optimizer *o);
+/* Optimizer::init — optim.rs:9,43-46,128-132: forgets the moments, step count back to 1 */
+sage_status sage_optimizer_init(sage_optimizer *o, sage_session *s);
+/* Optimizer::update(&grads, ctx) — optim.rs:11,48-93,134-177.  grads[i] = d loss / d params[i]
+ * (sage_grad); a gradient that the session has not evaluated yet is evaluated first, like the
+ * reference does (with its "inefficient" warning, optim.rs:56-59). */
+sage_status sage_optimizer_update(sage_optimizer *o, sage_session *s, sage_var *const *params, sage_var *const *grads, int32_t n);
+
 /* ---- models.  Bert — src/models/bert.rs:57-139; config fields mirror BertConfig (:8-55). */
 typedef struct {
     int64_t embed_dim, num_vocabs, max_num_tokens, hidden_dim, num_layers, num_heads, num_classes;

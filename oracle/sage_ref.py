@@ -13,8 +13,9 @@ floating-point contraction, which the tolerances in tests/ allow for).
 Parity status: pinned by the reference's own golden vectors for map, reduce,
 argmax, gemm, gather, slice/unslice/concat, im2col/col2im/conv_2d, relu,
 softmax, softmax_cross_entropy and max_pool_2d (tests/test_oracle_golden.py).
-layer_norm, matmul_batched, Bert and ResNet have no vector in the reference:
-parity unpinned there; this restatement is the arbiter.
+layer_norm, matmul_batched, Bert, ResNet, accuracy and the optimizers (Sgd,
+Adam) have no vector in the reference: parity unpinned there; this restatement
+is the arbiter.
 """
 import ctypes
 import heapq
@@ -609,6 +610,16 @@ class Scatter:
     def compute(self, x):  # core.rs:764-833
         t, ind = x
         assert t.dtype == FLOAT
+        if any(s == 0 and e > 1 for s, e in zip(ind.shape.strides, ind.shape.extents)):
+            # A broadcast index (Embedding's gradient: token ids expanded along the embedding axis).  The
+            # reference's kernel decomposes the work-item id by the index tensor's strides and divides
+            # by the zero stride (core.rs:795-806): there is no behaviour to restate, so the operator's
+            # definition is applied, y[.., ind[i], ..] += x[i], in work-item order.
+            y = np.zeros(self.extents, dtype=np.float32)
+            where = list(np.indices(ind.shape.extents))
+            where[self.axis] = ind.numpy().astype(np.int64)
+            np.add.at(y, tuple(where), t.numpy())
+            return Tensor(y.reshape(-1), Shape(self.extents), t.dtype)
         y = np.empty(int(np.prod(self.extents)), dtype=np.float32)
         _C.o_scatter(_ptr(t.buf), t.shape.rank(), _arr(t.shape.strides), ctypes.c_int64(t.shape.offset),
                      _ptr(ind.buf), _arr(ind.shape.extents), _arr(ind.shape.strides),
@@ -1133,3 +1144,81 @@ def resnet18(chan_input, num_classes):  # models/resnet.rs:74-129 with d18; Batc
         cin, cout = cout, cout * 2
     m.add(AdaptiveAvgPool2d([1, 1])).add(Flatten()).add(Dense(512, num_classes))
     return m
+
+
+# --------------------------------------------------------------------------- metric, optimizers
+def accuracy(logits, labels):  # ops/metric.rs:4-17
+    top = argmax(logits, 1, True)
+    return float_(sum_(eq(top, labels), [0], False)) / float(top.size())
+
+
+def grad_param(y, model):  # var.rs:46-54
+    params = model.params()
+    return dict(zip(params, grad(y, params)))
+
+
+def _f32(x):
+    return float(np.float32(x))
+
+
+class Sgd:  # optim.rs:14-94
+    """Only the plain rule is reachable in the reference: there is no setter for momentum, and with
+    momentum != 0 update() unwraps a buffer it never stored (optim.rs:68-69)."""
+
+    def __init__(self, lr):
+        self.lr, self.momentum, self.weight_decay = _f32(lr), 0.0, 0.0
+
+    def init(self):
+        pass
+
+    def update(self, grads):
+        """grads: {param Var: grad Var}; every gradient is evaluated against the old parameters first
+        (the reference runs its compiled program before update(), examples/train.rs:52-54)."""
+        assert self.momentum == 0.0, "unreachable in the reference"
+        keys = list(grads.keys())
+        values = evaluate([grads[p] for p in keys])
+        for p, gt in zip(keys, values):
+            assert p.op is None, "param is not data tensor"
+            g = Var.new(gt)
+            if self.weight_decay != 0.0:
+                g = g + p * self.weight_decay
+            p.set((p - g * self.lr).eval())  # optim.rs:82,90
+
+
+class Adam:  # optim.rs:97-178
+    """No tests or golden values exist for the optimizers in the reference: parity unpinned; the
+    restatement follows update() expression by expression, with the oracle's own map kernels."""
+
+    def __init__(self, lr):
+        self.lr, self.beta1, self.beta2, self.eps, self.weight_decay = _f32(lr), _f32(0.9), _f32(0.999), _f32(1e-08), 0.0
+        self.init()
+
+    def init(self):  # :128-132
+        self.m_t, self.v_t = {}, {}
+        self.t = Tensor.new(np.float32([1.0]))
+
+    def update(self, grads):
+        keys = list(grads.keys())
+        values = evaluate([grads[p] for p in keys])
+        t = Var.new(self.t)
+        for p, gt in zip(keys, values):
+            assert p.op is None, "param is not data tensor"
+            key = grads[p].uid
+            g = Var.new(gt)
+            if self.weight_decay != 0.0:
+                g = g + p * self.weight_decay
+            if key in self.m_t:  # :147-151
+                m = Var.new(self.m_t[key]) * self.beta1 + g * _f32(np.float32(1.0) - np.float32(self.beta1))
+            else:
+                m = scalar(0.0, p.extents)
+            self.m_t[key] = m.eval()
+            if key in self.v_t:  # :155-159
+                v = Var.new(self.v_t[key]) * self.beta2 + pow_(g, 2.0) * _f32(np.float32(1.0) - np.float32(self.beta2))
+            else:
+                v = scalar(0.0, p.extents)
+            self.v_t[key] = v.eval()
+            m, v = Var.new(self.m_t[key]), Var.new(self.v_t[key])
+            m_hat = m / (neg(pow_(scalar(self.beta1, [1]), t)) + 1.0)  # :168-169
+            v_hat = v / (neg(pow_(scalar(self.beta2, [1]), t)) + 1.0)
+            p.set((p - m_hat * self.lr / (sqrt(v_hat) + self.eps)).eval())  # :171-173
+        self.t = (t + 1.0).eval()  # :176

@@ -559,6 +559,62 @@ def grad(y, xs):
     return [Var(_P(h)) for h in out]
 
 
+def grad_param(y, model):
+    """grad_param(y, model) (var.rs:46-54): {parameter: gradient}, in Parameter::params order."""
+    params = model.params()
+    return dict(zip(params, grad(y, params)))
+
+
+def accuracy(logits, labels):
+    """ops::metric::accuracy (src/ops/metric.rs:4-17)."""
+    return _mk(lib.sage_op_accuracy, logits.h, labels.h)
+
+
+# --------------------------------------------------------------------------- optimizers (src/optim.rs)
+class Optimizer:
+    """trait Optimizer (optim.rs:8-12).  `update` takes the {parameter: gradient} map of grad_param."""
+
+    def __init__(self, handle):
+        self.h = handle
+
+    def __del__(self):
+        try:
+            lib.sage_optimizer_destroy(self.h)
+        except Exception:
+            pass
+
+    def init(self, ctx):
+        ctx._ck(lib.sage_optimizer_init(self.h, ctx.s))
+
+    def update(self, grads, ctx):
+        params = list(grads.keys())
+        p = (_P * len(params))(*[v.h for v in params])
+        g = (_P * len(params))(*[grads[v].h for v in params])
+        ctx._ck(lib.sage_optimizer_update(self.h, ctx.s, p, g, len(params)))
+
+    def set_weight_decay(self, weight_decay):
+        lib.sage_optimizer_set_weight_decay(self.h, ctypes.c_float(weight_decay))
+
+
+class Sgd(Optimizer):
+    """Sgd::new(lr) (optim.rs:28-40): param -= lr * grad."""
+
+    def __init__(self, lr):
+        h = _P()
+        _gck(lib.sage_sgd_create(ctypes.c_float(lr), ctypes.byref(h)))
+        super().__init__(h)
+
+
+class Adam(Optimizer):
+    """Adam::new(lr) (optim.rs:112-125): beta1 0.9, beta2 0.999, eps 1e-08; the first update of a
+    parameter only stores zero moments (optim.rs:147-159)."""
+
+    def __init__(self, lr):
+        h = _P()
+        _gck(lib.sage_adam_create(ctypes.c_float(lr), ctypes.byref(h)))
+        super().__init__(h)
+
+
 # --------------------------------------------------------------------------- models
 class Bert:
     """models::Bert (src/models/bert.rs:57-139).  Defaults are BertConfig::base()."""

@@ -6,6 +6,7 @@
 #include "../../../include/sage_graph.h"
 #include "../graph/graph.h"
 #include "../nn/nn.h"
+#include "../nn/optim.h"
 
 using namespace sage;
 
@@ -21,6 +22,10 @@ struct sage_bert {
 };
 struct sage_model {
     std::shared_ptr<nn::Sequential> impl;
+};
+
+struct sage_optimizer {
+    std::unique_ptr<nn::Optimizer> impl;
 };
 
 static thread_local std::string g_error;
@@ -284,6 +289,40 @@ sage_status sage_op_softmax_cross_entropy(const sage_var *x, const sage_var *lab
 sage_status sage_op_layer_norm(const sage_var *x, int32_t naxes, const int64_t *axes, const sage_var *gamma, const sage_var *beta, float eps,
                                sage_var **out) {
     OP(ops::layer_norm(x->v, axes_of(naxes, axes), gamma->v, beta->v, eps));
+}
+
+sage_status sage_op_accuracy(const sage_var *logits, const sage_var *labels, sage_var **out) { OP(ops::accuracy(logits->v, labels->v)); }
+
+// ---------------------------------------------------------------- optimizers
+sage_status sage_sgd_create(float lr, sage_optimizer **out) {
+    *out = new sage_optimizer{std::unique_ptr<nn::Optimizer>(new nn::Sgd(lr))};
+    return SAGE_OK;
+}
+sage_status sage_adam_create(float lr, sage_optimizer **out) {
+    *out = new sage_optimizer{std::unique_ptr<nn::Optimizer>(new nn::Adam(lr))};
+    return SAGE_OK;
+}
+sage_status sage_optimizer_set_weight_decay(sage_optimizer *o, float weight_decay) {
+    if (auto *a = dynamic_cast<nn::Adam *>(o->impl.get())) a->weight_decay = weight_decay;
+    else if (auto *g = dynamic_cast<nn::Sgd *>(o->impl.get())) g->weight_decay = weight_decay;
+    return SAGE_OK;
+}
+sage_status sage_optimizer_destroy(sage_optimizer *o) {
+    delete o;
+    return SAGE_OK;
+}
+sage_status sage_optimizer_init(sage_optimizer *o, sage_session *s) {
+    return guarded([&]() -> sage_status { return o->impl->init(*s->impl); });
+}
+sage_status sage_optimizer_update(sage_optimizer *o, sage_session *s, sage_var *const *params, sage_var *const *grads, int32_t n) {
+    return guarded([&]() -> sage_status {
+        std::vector<Var> p, g;
+        for (int i = 0; i < n; ++i) {
+            p.push_back(params[i]->v);
+            g.push_back(grads[i]->v);
+        }
+        return o->impl->update(p, g, *s->impl);
+    });
 }
 
 // ---------------------------------------------------------------- models

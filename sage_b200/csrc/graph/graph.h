@@ -248,6 +248,8 @@ Var softmax(const Var &x, const std::vector<long long> &axes);
 Var log_sum_exp(const Var &x, const std::vector<long long> &axes);
 Var softmax_cross_entropy(const Var &x, const Var &labels);
 Var layer_norm(const Var &x, const std::vector<long long> &axes, const Var &gamma, const Var &beta, float eps);
+// metric.rs
+Var accuracy(const Var &logits, const Var &labels);
 // arithmetic sugar (map.rs:1180-1370)
 inline Var add(const Var &a, const Var &b) { return binary_map(a, b, Add); }
 inline Var sub(const Var &a, const Var &b) { return binary_map(a, b, Sub); }

@@ -127,6 +127,12 @@ Var ops::softmax_cross_entropy(const Var &x1, const Var &x2) {  // nn.rs:70-82
     return neg(reduce(log_p, {1}, false, Sum));
 }
 
+Var ops::accuracy(const Var &logits, const Var &labels) {  // metric.rs:4-17
+    Var top = reduce_arg(logits, 1, true, true);
+    Var hits = reduce(binary_map(top, labels, Eq), {0}, false, Sum);
+    return div(unary_map(hits, CastFloat), (float)top.size());
+}
+
 Var ops::layer_norm(const Var &x, const std::vector<long long> &axes_in, const Var &gamma, const Var &beta, float eps) {
     std::vector<int> axes = to_axes(axes_in, x.rank());  // nn.rs:84-100
     Var m = mean(x, axes_in, true);

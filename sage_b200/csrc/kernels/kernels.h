@@ -148,5 +148,29 @@ sage_status gemm_simt(Context &ctx, const GemmArgs &g);
 sage_status gemm_tcgen05(Context &ctx, const GemmArgs &g);
 sage_status gemm(Context &ctx, const GemmArgs &g);  // picks per ctx.opts().gemm_backend
 
+// optim.cu — Sgd::update / Adam::update (src/optim.rs:42-94, 125-178), many parameters per launch.
+// A slot: parameter `p` (n contiguous floats, updated in place), gradient `g`, Adam's moments `m`, `v`
+// (updated in place; null for Sgd), and optionally the parameter's whole-storage tf32 planes (`hi`, lo
+// `plane` floats further) which receive the split of the new value.  `first` = this parameter's first
+// update: Adam stores zero moments then.  `vec` is filled in by the launcher.
+constexpr int kOptSlots = 32;
+struct OptSlot {
+    float *p = nullptr;
+    const float *g = nullptr;
+    float *m = nullptr, *v = nullptr;
+    float *hi = nullptr;
+    long long plane = 0, n = 0;
+    int first = 0, vec = 0;
+};
+struct OptSgd {
+    float lr = 0.f, weight_decay = 0.f;
+};
+struct OptAdam {
+    float lr = 0.f, beta1 = 0.9f, beta2 = 0.999f, one_minus_beta1 = 0.f, one_minus_beta2 = 0.f, eps = 1e-08f, weight_decay = 0.f;
+    float corr1 = 1.f, corr2 = 1.f;  // -(beta1 ^ t) + 1 and -(beta2 ^ t) + 1 for this step's t
+};
+sage_status sgd_update(Context &ctx, const OptSlot *slots, int count, const OptSgd &k);
+sage_status adam_update(Context &ctx, const OptSlot *slots, int count, const OptAdam &k);
+
 }  // namespace k
 }  // namespace sage

@@ -13,6 +13,8 @@
 // ref_compat the group result is combined with that 0 once at the end, which is the same value.
 #include <cuda_runtime.h>
 
+#include <algorithm>
+
 #include "kernels.h"
 #include "launch.h"
 
@@ -211,6 +213,72 @@ static RDims canonical_inner(const Dims &in) {
     return r;
 }
 
+// Column reduction: x is [rows, cols] with unit column stride and `pitch` elements between rows; y[c]
+// combines x[r, c] over the rows of this block's chunk (blockIdx.y).  A warp reads 32 consecutive
+// columns of a row (one 128-byte line); the 8 warps of a block take rows 8 apart, four rows in flight
+// each.  With more than one chunk the partial results go to scratch [chunks, cols] and a second launch
+// of the same kernel combines them: the order of combination is fixed, so results repeat bit for bit.
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_cols_kernel(const T *__restrict__ x, T *__restrict__ y, long long rows, long long cols,
+                                                          long long pitch, long long rows_per_chunk, int kind, int ref_compat) {
+    grid_dependency_sync();
+    __shared__ T part[8][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const long long col = (long long)blockIdx.x * 32 + tx;
+    const long long r0 = (long long)blockIdx.y * rows_per_chunk;
+    const long long r1 = r0 + rows_per_chunk < rows ? r0 + rows_per_chunk : rows;
+    T acc = Ops<T>::identity(kind), a1 = acc, a2 = acc, a3 = acc;
+    if (col < cols) {
+        const T *base = x + col;
+        long long r = r0 + ty;
+        for (; r + 24 < r1; r += 32) {
+            const T v0 = base[r * pitch], v1 = base[(r + 8) * pitch], v2 = base[(r + 16) * pitch], v3 = base[(r + 24) * pitch];
+            acc = Ops<T>::apply(kind, acc, v0);
+            a1 = Ops<T>::apply(kind, a1, v1);
+            a2 = Ops<T>::apply(kind, a2, v2);
+            a3 = Ops<T>::apply(kind, a3, v3);
+        }
+        for (; r < r1; r += 8) acc = Ops<T>::apply(kind, acc, base[r * pitch]);
+        acc = Ops<T>::apply(kind, Ops<T>::apply(kind, acc, a1), Ops<T>::apply(kind, a2, a3));
+    }
+    part[ty][tx] = acc;
+    __syncthreads();
+    if (ty == 0 && col < cols) {
+#pragma unroll
+        for (int i = 1; i < 8; ++i) acc = Ops<T>::apply(kind, acc, part[i][tx]);
+        if (ref_compat) acc = Ops<T>::apply(kind, (T)0, acc);
+        y[(long long)blockIdx.y * cols + col] = acc;
+    }
+}
+
+template <typename T>
+static sage_status launch_reduce_cols(Context &ctx, int kind, const T *x, long long rows, long long cols, long long pitch, T *y) {
+    const int compat = ctx.opts().ref_compat;
+    const long long tiles = (cols + 31) / 32;
+    long long chunks = (2LL * ctx.sm_count + tiles - 1) / tiles;
+    chunks = std::max(1LL, std::min(chunks, rows / 64));
+    ctx.note_launch("reduce_cols");
+    if (chunks > 1) ctx.note_launch("reduce_cols");
+    if (ctx.dry()) return SAGE_OK;
+    if (chunks == 1) {
+        launch_dependent(ctx.pdl, ctx.stream(), reduce_cols_kernel<T>, dim3((unsigned)tiles, 1), dim3(256), 0, x, y, rows, cols, pitch, rows, kind, compat);
+        return ctx.check_cuda(cudaGetLastError(), "reduce_cols launch");
+    }
+    const long long per = (rows + chunks - 1) / chunks;
+    chunks = (rows + per - 1) / per;
+    Block *scratch = ctx.allocator().alloc((size_t)(chunks * cols) * sizeof(T));
+    if (!scratch) return ctx.fail(SAGE_ERR_OOM, "out of memory for the partial results of a column reduction");
+    T *partial = reinterpret_cast<T *>(scratch->ptr);
+    // the accumulator rule (start from 0) is applied once, by the second stage
+    launch_dependent(ctx.pdl, ctx.stream(), reduce_cols_kernel<T>, dim3((unsigned)tiles, (unsigned)chunks), dim3(256), 0, x, partial, rows, cols, pitch, per,
+                     kind, 0);
+    launch_dependent(ctx.pdl, ctx.stream(), reduce_cols_kernel<T>, dim3((unsigned)tiles, 1), dim3(256), 0, (const T *)partial, y, chunks, cols, cols, chunks,
+                     kind, compat);
+    sage_status st = ctx.check_cuda(cudaGetLastError(), "reduce_cols launch");
+    ctx.allocator().free(scratch);  // stream-ordered: reused only by work enqueued after the second stage
+    return st;
+}
+
 template <typename T>
 static sage_status launch_reduce(Context &ctx, int kind, const T *x, const Dims &outer_in, const Dims &inner_in, T *y) {
     RDims outer;
@@ -229,6 +297,9 @@ static sage_status launch_reduce(Context &ctx, int kind, const T *x, const Dims 
     for (int i = 0; i < inner.ndim; ++i) n_in *= inner.ext[i];
     if (n_out == 0) return SAGE_OK;
     const bool inner_contig = inner.str[inner.ndim - 1] == 1;
+    // [rows, cols] -> [cols] (bias gradients, sums over the batch): the kept axis is the contiguous one
+    if (outer_in.ndim == 1 && outer_in.str[0] == 1 && inner.ndim == 1 && inner.str[0] >= n_out && n_out >= 2 && n_in >= 64 && n_out <= (1LL << 31))
+        return launch_reduce_cols<T>(ctx, kind, x, n_in, n_out, inner.str[0], y);
     int G = 1;
     if (inner_contig && n_in >= 64) G = (n_in >= 8192 || n_out < 2LL * ctx.sm_count) ? 256 : 32;
     // A column reduction with very few outputs would leave the GPU idle; a CTA per output is
