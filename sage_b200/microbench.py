@@ -7,6 +7,7 @@ row kernels and f32-equivalent TFLOP/s of the tensor-core GEMM, each as one JSON
   python -m sage_b200.microbench --case config1 --rows 16384 --cols 4096  # whole forward + grad graph
   python -m sage_b200.microbench --case all
   python -m sage_b200.microbench --case train_resnet --batch 128             # examples/train.rs: one Adam step of ResNet-18
+  python -m sage_b200.microbench --case train_bert                           # one Adam step of Bert base, batch 32 x 128 tokens
   python -m sage_b200.microbench --case tf32_peak                          # library TF32 GEMM: the tensor-pipe denominator
 
 Times are device times from CUDA events recorded on the context's stream in front of every launch
@@ -156,6 +157,54 @@ def case_train_resnet(ctx, a):
             "kernel_ms": {k: [n, round(t, 4)] for k, (n, t) in top}, "profiled_step_ms": total}
 
 
+def case_train_bert(ctx, a):
+    """One Adam step of sage's Bert (BertConfig::base(), batch 32, 128 tokens, 2 classes): loss = mean softmax
+    cross entropy of the logits, gradients of all parameters, Optimizer::update.  Token ids / mask / labels are
+    uploaded and the loss read back every step."""
+    batch, seq = (a.batch if a.batch > 1 else 32), 128
+    rng = np.random.default_rng(6002)
+    model = S.Bert()
+    for p in model.params():
+        ctx.set(p, (rng.standard_normal(p.extents) * 0.02).astype(np.float32))
+    ids, mask, lab = S.Var.empty([batch, seq], S.U32), S.Var.empty([batch, seq]), S.Var.empty([batch, 1], S.U32)
+    logits = model.pass_(ids, mask)
+    loss = S.softmax_cross_entropy(logits, lab).mean([0], False)
+    grads = S.grad_param(loss, model)
+    opt = S.Adam(1e-4)
+    opt.init(ctx)
+    h_ids, h_mask, h_lab = ctx.pinned((batch, seq), np.uint32), ctx.pinned((batch, seq), np.float32), ctx.pinned((batch, 1), np.uint32)
+    h_ids[...] = rng.integers(0, 30522, h_ids.shape)
+    h_mask[...] = 1.0
+    h_lab[...] = rng.integers(0, 2, h_lab.shape)
+    targets = list(grads.values()) + [loss]
+    last = {}
+
+    def step():
+        ctx.set(ids, None, pinned_ptr=h_ids.ctypes.data)
+        ctx.set(mask, None, pinned_ptr=h_mask.ctypes.data)
+        ctx.set(lab, None, pinned_ptr=h_lab.ctypes.data)
+        ctx.eval(*targets)
+        opt.update(grads, ctx)
+        last["loss"] = float(ctx.read(loss)[0])
+        ctx.clear()
+    for _ in range(3):
+        step()
+    first_loss = last["loss"]
+    ctx.sync()
+    ctx.timer_start()
+    for _ in range(a.reps):
+        step()
+    ms = ctx.timer_stop() / a.reps
+    ctx.profile_begin()
+    step()
+    prof = ctx.profile_end()
+    top = sorted(prof.items(), key=lambda kv: -kv[1][1])[:10]
+    return {"case": "train_bert_base", "batch": batch, "seq": seq, "ms_per_step": ms, "sequences_per_s": batch / (ms * 1e-3),
+            "launches_per_step": sum(n for n, t in prof.values()), "loss_after_3_steps": first_loss, "loss_now": last["loss"],
+            "kernel_ms": {k: [n, round(t, 4)] for k, (n, t) in top}, "profiled_step_ms": sum(t for n, t in prof.values()),
+            "mem_peak_gb": ctx.mem_stats()["mem_peak"] / 1e9}
+
+
 def case_tf32_peak(a):
     """The tensor-pipe denominator for 3xTF32: the library TF32 GEMM (torch.matmul with TF32 allowed) at
     8192^3, measured like the bf16 figure of MEASURED_PEAKS.json — a burst of 10 and a loop of ~3 s."""
@@ -211,6 +260,8 @@ def main():
             r = case_config1(ctx, a)
         elif c == "train_resnet":
             r = case_train_resnet(ctx, a)
+        elif c == "train_bert":
+            r = case_train_bert(ctx, a)
         else:
             r = row_case(ctx, a, c)
         print(json.dumps(r), flush=True)

@@ -360,7 +360,8 @@ def gemm_err(got, ref):
     return float((np.abs(a - b) / np.maximum(np.abs(b), rms)).max())
 
 
-@pytest.mark.parametrize("m,n,k", [(1024, 1024, 1024), (1, 1, 1), (7, 13, 5), (129, 257, 63), (128, 768, 3072), (300, 2, 768)])
+@pytest.mark.parametrize("m,n,k", [(1024, 1024, 1024), (1, 1, 1), (7, 13, 5), (129, 257, 63), (128, 768, 3072), (300, 2, 768),
+                                   (576, 64, 6272), (128, 512, 4608), (64, 128, 2052)])  # the last three: split over K
 def test_matmul_vs_oracle(ctx, m, n, k):
     rng = np.random.default_rng(2001)
     a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
@@ -372,10 +373,10 @@ def test_matmul_vs_oracle(ctx, m, n, k):
     assert np.linalg.norm(got - f64) / max(np.linalg.norm(f64), 1e-30) <= 2e-6
 
 
+@pytest.mark.parametrize("m,n,k", [(200, 136, 72), (320, 72, 4480)])  # the second: few tiles, long K, split over K
 @pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
-def test_gemm_transposes_vs_oracle(ctx, ta, tb):
+def test_gemm_transposes_vs_oracle(ctx, ta, tb, m, n, k):
     rng = np.random.default_rng(2002)
-    m, n, k = 200, 136, 72
     a = rng.uniform(-1, 1, (k, m) if ta else (m, k)).astype(np.float32)
     b = rng.uniform(-1, 1, (n, k) if tb else (k, n)).astype(np.float32)
     got = S.gemm(ctx.var(a), ctx.var(b), ta, tb).eval(ctx)
