@@ -1,9 +1,10 @@
 // Whole-row programs: analysis of the graph, CUDA C generation, launch.  See rowfuse.h.
 //
-// Value classes over the common [R, C] space:
-//   Full    [R, C]                 C values per row, spread over the block's threads in registers
-//   Row     [R, 1] or [R]          one value per row, held by every thread
-//   Scalar  one element            one value, held by every thread
+// Value classes over the common row space (R rows of C contiguous elements; a tensor of any rank whose
+// last axis has C elements and whose leading axes multiply to R is such a space, e.g. [32, 128, 768]):
+//   Full    R * C elements, last extent C     C values per row, spread over the block's threads in registers
+//   Row     R elements ([.., 1] or [..])      one value per row, held by every thread
+//   Scalar  one element                       one value, held by every thread
 // Operators accepted (anything else makes the graph ineligible and the evaluator compiles it the
 // ordinary way): maps (src/ops/map.rs) whose operands are of the output's class or broadcast into it;
 // reshape / expand / squeeze / unsqueeze that keep a value per-row or per-graph (src/ops/core.rs:203-476;
@@ -36,6 +37,7 @@ struct Val {
     std::string expr;  // KMap: C expression over x0..xn
     int red = 0;       // KReduce: ops::Red
     int input = -1, output = -1;
+    bool bcast_leaf = false;  // KLeaf: a Full-shaped view with last stride 0, read as a value per row
 };
 
 const char *ctype(int dt) { return dt == SAGE_F32 ? "float" : dt == SAGE_I32 ? "int" : "uint"; }
@@ -45,8 +47,8 @@ bool classify(const Array &e, long long R, long long C, Cls *c) {
     long long size = 1;
     for (long long x : e) size *= x;
     if (size == 1) *c = Scalar;
-    else if (e.size() == 2 && e[0] == R && e[1] == C) *c = Full;
-    else if ((e.size() == 2 && e[0] == R && e[1] == 1) || (e.size() == 1 && e[0] == R)) *c = Row;
+    else if (size == R * C && e.back() == C) *c = Full;
+    else if (size == R) *c = Row;  // R != R * C and a Full value has more elements, so the three cases are disjoint
     else return false;
     return true;
 }
@@ -102,6 +104,19 @@ struct Builder {
         if (v.is_data() || evaluated.count(v.key())) {
             val.kind = KLeaf;
             val.input = (int)p.in_val.size();
+            // A materialised view that repeats one value along the row (expand of a [.., 1] tensor: the state
+            // keeps the source's buffer, last stride 0): read as one value per row, never copied out.
+            const Shape &sh = v.desc.shape;
+            if (val.cls == Full && sh.strides.back() == 0) {
+                Array lead(sh.extents.begin(), sh.extents.end() - 1);
+                const Array dflt = Shape::default_strides(lead);
+                bool rows_contiguous = true;
+                for (size_t i = 0; i < lead.size(); ++i)
+                    if (lead[i] > 1 && sh.strides[i] != dflt[i]) rows_contiguous = false;
+                if (!rows_contiguous) return fail();
+                val.cls = Row;
+                val.bcast_leaf = true;
+            }
         } else {
             const Operator &op = *v.origin->op;
             const std::vector<Var> &in = v.origin->inputs;
@@ -121,30 +136,35 @@ struct Builder {
                 ++p.n_map;
             } else if ((vk = view_op_kind(op)) >= 0) {
                 if (vk == 2 || vk == 5) return fail();  // permute, slice
-                // expand: only from a value per row / per graph laid out as [R, 1] or one element
                 const Array &ie = in[0].extents();
-                if (vk == 1 && !(in[0].size() == 1 || (ie.size() == 2 && ie[0] == p.rows && ie[1] == 1))) return fail();
-                if (vk != 1 && p.vals[val.args[0]].cls != val.cls) return fail();
-                if (vk != 1 && val.cls == Full && ie != v.extents()) return fail();
+                if (vk == 1) {
+                    // expand: from one element, or from a value per row laid out with a trailing unit axis
+                    // (a vector along the row axis, e.g. a bias [C], has R == C elements at most by accident)
+                    if (!(in[0].size() == 1 || (in[0].size() == p.rows && ie.back() == 1))) return fail();
+                } else if (p.vals[val.args[0]].cls != val.cls) {
+                    return fail();  // reshape / squeeze / unsqueeze keep a value in its class (rows stay rows)
+                }
                 val.kind = KAlias;
                 val.cls = cls_of(0);
             } else if (reduce_op_info(op, &red_kind, &axes)) {
-                if (v.dtype() != SAGE_F32 || in[0].rank() != 2 || axes.size() != 1 || axes[0] != 1 || in[0].extent(0) != p.rows) return fail();
-                // the operand really has the extents the operator sees (not a broadcast standing for them)
-                if (in[0].extent(1) == p.cols ? cls_of(0) != Full : in[0].extent(1) != 1) return fail();
-                if (val.cls == Scalar) return fail();
+                const Array &ie = in[0].extents();
+                if (v.dtype() != SAGE_F32 || axes.size() != 1 || axes[0] != in[0].rank() - 1 || val.cls != Row) return fail();
+                // over the row axis of a Full value (which really has those extents: not a broadcast standing
+                // for them), or over the trailing unit axis of a value per row
+                if (in[0].size() == p.rows * p.cols ? (ie.back() != p.cols || cls_of(0) != Full) : (in[0].size() != p.rows || ie.back() != 1))
+                    return fail();
                 val.kind = KReduce;
                 val.red = red_kind;
                 ++p.n_reduce;
-            } else if (index_op_axis(op, false) == 1) {
+            } else if (index_op_axis(op, false) == in[0].rank() - 1 && index_op_axis(op, false) >= 0) {
                 const Array &ie = in[1].extents();
-                if (in[0].rank() != 2 || in[0].extent(1) != p.cols || cls_of(0) != Full || ie.size() != 2 || ie[0] != p.rows || ie[1] != 1)
+                if (in[0].size() != p.rows * p.cols || in[0].extents().back() != p.cols || cls_of(0) != Full || in[1].size() != p.rows || ie.back() != 1)
                     return fail();
                 val.kind = KGather;
                 ++p.n_index;
-            } else if (index_op_axis(op, true) == 1) {
+            } else if (index_op_axis(op, true) == in[0].rank() - 1 && index_op_axis(op, true) >= 0) {
                 const Array &ie = in[1].extents();
-                if (val.cls != Full || v.dtype() != SAGE_F32 || ie.size() != 2 || ie[0] != p.rows || ie[1] != 1 || cls_of(0) == Full) return fail();
+                if (val.cls != Full || v.dtype() != SAGE_F32 || in[1].size() != p.rows || ie.back() != 1 || cls_of(0) == Full) return fail();
                 val.kind = KScatter;
                 ++p.n_index;
             } else {
@@ -160,26 +180,21 @@ struct Builder {
 };
 
 // Cheap screen before any allocation: every operator below the targets is of an accepted family, and
-// the graph is small.  Also finds the [R, C] space: the extents of the first rank-2 value with C > 1.
-bool screen(const std::vector<Var> &targets, const std::unordered_set<Origin *> &evaluated, long long *R, long long *C) {
+// the graph is small.  Also finds the row space: the largest value is a Full one, its last extent is C.
+bool screen(const std::vector<Var> &targets, const std::unordered_set<Origin *> &evaluated, bool maps_suffice, long long *R, long long *C) {
     std::unordered_set<Origin *> seen;
     std::vector<Var> stack = targets;
-    bool found = false, reduces = false;
+    bool reduces = false;
+    long long largest = 0;
     while (!stack.empty()) {
         Var v = stack.back();
         stack.pop_back();
         if (!seen.insert(v.key()).second) continue;
         if (seen.size() > kMaxValues) return false;
-        if (v.rank() == 2 && v.extent(0) > 1 && v.extent(1) > 1) {
-            if (!found) {
-                *R = v.extent(0);
-                *C = v.extent(1);
-                found = true;
-            } else if (*R != v.extent(0) || *C != v.extent(1)) {
-                return false;
-            }
-        } else if (v.rank() > 2) {
-            return false;
+        if (v.size() > largest && v.rank() >= 1) {
+            largest = v.size();
+            *C = v.extents().back();
+            *R = largest / *C;
         }
         if (v.is_data() || evaluated.count(v.key())) continue;
         const Operator &op = *v.origin->op;
@@ -190,7 +205,7 @@ bool screen(const std::vector<Var> &targets, const std::unordered_set<Origin *> 
         else if (!map_expr_of(op) && view_op_kind(op) < 0) return false;
         for (const Var &a : v.origin->inputs) stack.push_back(a);
     }
-    return found && reduces;
+    return largest > 0 && *R > 1 && *C > 1 && (reduces || maps_suffice);
 }
 
 void emit(RowProgram &p) {
@@ -257,7 +272,9 @@ SG void rp_prefetch(const RowP &p, long long row, uint4 *stage);
         if (bytes <= 96 * 1024) p.stage_bytes = (uint32_t)bytes;
     }
     s << "#define RP_STAGE " << (size_t)n_stage * p.nv * p.threads << "\n";
-    s << "extern \"C\" __global__ void __launch_bounds__(RP_T) sage_row_program(const RowP p) {\n"
+    // at least as many blocks per SM as ~80 registers per thread allow: more warps to hide the latency of
+    // exp, shared memory and shuffles (the kernels run at low occupancy by construction)
+    s << "extern \"C\" __global__ void __launch_bounds__(RP_T, " << std::max(1, 65536 / (p.threads * 80)) << ") sage_row_program(const RowP p) {\n"
       << "  asm volatile(\"griddepcontrol.launch_dependents;\" ::: \"memory\");\n"
       << "  asm volatile(\"griddepcontrol.wait;\" ::: \"memory\");\n"
       << "  __shared__ float sh[2][" << std::max(1, n_red) << "][32];\n  __shared__ uint sh_pick[2][" << std::max(1, n_pick) << "];\n";
@@ -371,12 +388,12 @@ SG void rp_prefetch(const RowP &p, long long row, uint4 *stage);
 
 }  // namespace
 
-std::shared_ptr<RowProgram> row_program_build(const std::vector<Var> &evaluated, const std::vector<Var> &targets) {
+std::shared_ptr<RowProgram> row_program_build(const std::vector<Var> &evaluated, const std::vector<Var> &targets, bool whole_program, bool emit_source) {
     std::unordered_set<Origin *> ev;
     for (const Var &v : evaluated) ev.insert(v.key());
     long long R = 0, C = 0;
-    if (!screen(targets, ev, &R, &C)) return nullptr;
-    if (C < 128 || C > 16384) return nullptr;
+    if (!screen(targets, ev, !whole_program, &R, &C)) return nullptr;
+    if (C < 32 || C > 16384) return nullptr;
     auto p = std::make_shared<RowProgram>();
     p->rows = R;
     p->cols = C;
@@ -391,7 +408,7 @@ std::shared_ptr<RowProgram> row_program_build(const std::vector<Var> &evaluated,
     }
     bool full_leaf = false;
     for (int id : p->in_val) full_leaf = full_leaf || p->vals[id].cls == Full;
-    if (!full_leaf || p->n_reduce + p->n_index == 0) return nullptr;
+    if (whole_program && (!full_leaf || p->n_reduce + p->n_index == 0)) return nullptr;
     // Distribution of a row over the block: 128-bit accesses when the rows allow.  Elements per thread:
     // a block reduction costs every thread ~20 instructions whatever it holds, so few threads with
     // many elements keep the instruction count per element low (these kernels are as close to the
@@ -408,6 +425,7 @@ std::shared_ptr<RowProgram> row_program_build(const std::vector<Var> &evaluated,
     }
     if (p->nv * p->vec > 32) return nullptr;
     p->threads = (int)((t + 31) / 32 * 32);
+    if (!emit_source) return p;  // analysis only: is the graph a row program, and over which space
     emit(*p);
     if (const char *path = getenv("SAGE_ROW_PROGRAM_DUMP")) {  // diagnostics: the generated source
         if (FILE *f = fopen(path, "w")) {
@@ -433,7 +451,32 @@ std::string row_program_describe(const RowProgram &p) {
     return s.str();
 }
 
+void row_program_space(const RowProgram &p, long long *rows, long long *cols) {
+    *rows = p.rows;
+    *cols = p.cols;
+}
+
+int row_program_exchanges(const RowProgram &p) { return p.n_reduce + p.n_index; }
+
+std::vector<Var> row_program_inputs(const RowProgram &p) {
+    std::vector<Var> v;
+    for (int id : p.in_val) v.push_back(p.vals[id].var);
+    return v;
+}
+
 sage_status row_program_exec(RowProgram &p, Context &ctx, Session &s) {
+    std::vector<Tensor> outs;
+    sage_status st = row_program_run(p, ctx, [&](const Var &v, Tensor *t) { return s.get(v, t); }, &outs);
+    if (st) return st;
+    for (size_t i = 0; i < p.out_val.size(); ++i) {
+        const Var &v = p.vals[p.out_val[i]].var;
+        s.data[v.key()] = std::make_pair(v, outs[i]);
+    }
+    return SAGE_OK;
+}
+
+sage_status row_program_run(RowProgram &p, Context &ctx, const std::function<bool(const Var &, Tensor *)> &fetch, std::vector<Tensor> *outs_) {
+    if (p.source.empty()) return ctx.fail(SAGE_ERR_INVALID, "internal: row program was built for analysis only");
     if (p.owner != &ctx) {
         sage_status st = ctx.module_get(p.source, &p.module);
         if (st) return st;
@@ -452,12 +495,14 @@ sage_status row_program_exec(RowProgram &p, Context &ctx, Session &s) {
             if (!t.defined()) return ctx.fail(SAGE_ERR_INVALID, "a data variable of the program holds no tensor");
             sage_status st = t.to_device(ctx);
             if (st) return st;
-        } else if (!s.get(v.var, &t)) {
+        } else if (!fetch(v.var, &t)) {
             return ctx.fail(SAGE_ERR_INVALID, "internal: row program input not available");
         }
         if (t.data->planes_only) return ctx.fail(SAGE_ERR_INVALID, "internal: row program input exists as tf32 planes only");
         const bool aligned = p.vec == 1 || v.cls != Full || reinterpret_cast<uintptr_t>(t.ptr()) % 16 == 0;
-        if (!t.desc.shape.has_default_strides() || !aligned) {  // a strided view: gather it into a contiguous buffer first
+        if (v.bcast_leaf) {
+            if (t.desc.shape.strides != v.var.desc.shape.strides) return ctx.fail(SAGE_ERR_INVALID, "internal: a broadcast view arrived with other strides");
+        } else if (!t.desc.shape.has_default_strides() || !aligned) {  // a strided view: gather it into a contiguous buffer first
             Tensor c;
             sage_status st = Tensor::uninit(ctx, t.desc, &c);
             if (st) return st;
@@ -468,7 +513,8 @@ sage_status row_program_exec(RowProgram &p, Context &ctx, Session &s) {
         keep.push_back(t);
         pb[2 + i] = (uint64_t)reinterpret_cast<uintptr_t>(t.ptr());
     }
-    std::vector<Tensor> outs(p.out_val.size());
+    std::vector<Tensor> &outs = *outs_;
+    outs.assign(p.out_val.size(), Tensor());
     for (size_t i = 0; i < p.out_val.size(); ++i) {
         sage_status st = Tensor::uninit(ctx, p.vals[p.out_val[i]].var.desc, &outs[i]);
         if (st) return st;
@@ -478,13 +524,7 @@ sage_status row_program_exec(RowProgram &p, Context &ctx, Session &s) {
     const uint32_t grid[3] = {(uint32_t)std::min<long long>(p.rows, resident), 1, 1};
     const uint32_t block[3] = {(uint32_t)p.threads, 1, 1};
     void *params[1] = {pb.data()};
-    sage_status st = ctx.launch(p.module, "sage_row_program", grid, block, p.stage_bytes, params, nullptr, true);
-    if (st) return st;
-    for (size_t i = 0; i < p.out_val.size(); ++i) {
-        const Var &v = p.vals[p.out_val[i]].var;
-        s.data[v.key()] = std::make_pair(v, outs[i]);
-    }
-    return SAGE_OK;
+    return ctx.launch(p.module, "sage_row_program", grid, block, p.stage_bytes, params, nullptr, true);
 }
 
 }  // namespace sage

@@ -9,6 +9,7 @@
 // order (block reductions where the graph reduces along the row), and writes only the requested
 // outputs.  DRAM traffic is the compulsory one: inputs once, outputs once.
 #pragma once
+#include <functional>
 #include <memory>
 #include <string>
 #include <vector>
@@ -20,9 +21,18 @@ namespace sage {
 struct RowProgram;
 
 // Null when the graph below `targets` (cut at `evaluated` and at data variables) is not a row program.
-std::shared_ptr<RowProgram> row_program_build(const std::vector<Var> &evaluated, const std::vector<Var> &targets);
+// `whole_program`: the targets are a whole evaluation; then a graph of maps alone is left to the
+// ordinary map kernels (they already run at the HBM peak).  Without it (a region inside a larger
+// program) maps alone qualify.  `emit_source` false: analysis only, the result cannot be run.
+std::shared_ptr<RowProgram> row_program_build(const std::vector<Var> &evaluated, const std::vector<Var> &targets, bool whole_program = true,
+                                              bool emit_source = true);
 // Allocates the targets, launches the kernel, stores the results in `s.data`.
 sage_status row_program_exec(RowProgram &p, Context &ctx, Session &s);
+// The same with the caller's own lookup of the (non-data) inputs; `outs` are the targets in order.
+sage_status row_program_run(RowProgram &p, Context &ctx, const std::function<bool(const Var &, Tensor *)> &fetch, std::vector<Tensor> *outs);
+void row_program_space(const RowProgram &p, long long *rows, long long *cols);
+std::vector<Var> row_program_inputs(const RowProgram &p);
+int row_program_exchanges(const RowProgram &p);  // reductions + gathers + scatters in the program
 // Are the evaluated values the program was cut at still held by the session?
 bool row_program_ready(const RowProgram &p, const Session &s);
 std::string row_program_describe(const RowProgram &p);

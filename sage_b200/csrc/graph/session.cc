@@ -67,6 +67,10 @@ struct Routine {
     Var output;
     Node root;
     double exec_time = 0.0;
+    // A row group (rowfuse.h): several states of one [R, C] space computed by one generated kernel.  The
+    // same routine is registered under every state in `row_outputs`; running it once yields them all.
+    std::shared_ptr<RowProgram> row;
+    std::vector<Var> row_outputs;
 };
 
 struct Program {
@@ -328,8 +332,98 @@ static void mark_plane_readers(Node &n, bool tc, std::unordered_set<Origin *> *s
     }
 }
 
+// ------------------------------------------------------------------------------ row groups
+// States whose bodies stay inside one [R, C] row space (maps, axis-1 reductions, gather / scatter along
+// the row) and that feed one another are merged into one generated kernel: the values between them
+// never travel through DRAM.  `order` is topological; `inputs[k]` lists what state k reads.
+struct RowGroupPlan {
+    std::vector<int> members;  // indices into `order`
+};
+
+static std::vector<RowGroupPlan> plan_row_groups(const std::vector<Var> &order, const std::unordered_map<Origin *, std::vector<Var>> &inputs) {
+    const int n = (int)order.size();
+    std::vector<RowGroupPlan> plans;
+    if (n < 2 || n > 8192) return plans;
+    std::unordered_map<Origin *, int> index;
+    for (int i = 0; i < n; ++i) index[order[i].key()] = i;
+    const int words = (n + 63) / 64;
+    std::vector<std::vector<uint64_t>> anc(n, std::vector<uint64_t>(words, 0));  // states that state i depends on
+    std::vector<std::vector<int>> reads(n);
+    std::vector<long long> R(n, 0), C(n, 0);
+    std::vector<char> ok(n, 0), exchanges(n, 0);
+    for (int i = 0; i < n; ++i) {
+        const std::vector<Var> &in = inputs.at(order[i].key());
+        for (const Var &v : in) {
+            auto it = index.find(v.key());
+            if (it == index.end()) continue;
+            reads[i].push_back(it->second);
+            anc[i][it->second / 64] |= 1ull << (it->second % 64);
+            for (int w = 0; w < words; ++w) anc[i][w] |= anc[it->second][w];
+        }
+        if (auto probe = row_program_build(in, {order[i]}, false, false)) {
+            ok[i] = 1;
+            exchanges[i] = row_program_exchanges(*probe) > 0;
+            row_program_space(*probe, &R[i], &C[i]);
+        }
+        if (getenv("SAGE_ROW_GROUP_DEBUG")) {
+            std::string e;
+            for (long long x : order[i].extents()) e += std::to_string(x) + ",";
+            fprintf(stderr, "state %d %s [%s] ok=%d space=%lldx%lld reads=%zu\n", i, order[i].origin->op->name(), e.c_str(), (int)ok[i], R[i], C[i], in.size());
+        }
+    }
+    std::vector<int> group(n);
+    std::vector<std::vector<int>> members(n);
+    for (int i = 0; i < n; ++i) {
+        group[i] = i;
+        members[i] = {i};
+    }
+    auto in_set = [&](const std::vector<uint64_t> &set, int i) { return (set[i / 64] >> (i % 64)) & 1; };
+    // May groups P and Q become one routine?  Not if some state outside them lies between them (it would
+    // have to run both after and before the merged routine).
+    auto legal = [&](int P, int Q) {
+        std::vector<uint64_t> u(words, 0), au(words, 0);
+        for (int g : {P, Q})
+            for (int m : members[g]) {
+                u[m / 64] |= 1ull << (m % 64);
+                for (int w = 0; w < words; ++w) au[w] |= anc[m][w];
+            }
+        if (members[P].size() + members[Q].size() > 24) return false;  // keeps the register arrays of one kernel in hand
+        for (int x = 0; x < n; ++x) {
+            if (!in_set(au, x) || in_set(u, x)) continue;
+            for (int w = 0; w < words; ++w)
+                if (anc[x][w] & u[w]) return false;
+        }
+        return true;
+    };
+    for (int i = 0; i < n; ++i) {
+        if (!ok[i]) continue;
+        for (int j : reads[i]) {
+            if (!ok[j] || R[j] != R[i] || C[j] != C[i]) continue;
+            const int P = group[j], Q = group[i];
+            if (P == Q || !legal(P, Q)) continue;
+            for (int m : members[Q]) {
+                group[m] = P;
+                members[P].push_back(m);
+            }
+            members[Q].clear();
+        }
+    }
+    // a state on its own is worth a generated kernel when its body reduces (it would otherwise run as
+    // several kernels); a lone map chain already is one kernel, and a lone softmax / log_sum_exp /
+    // layer_norm has its hand-written kernel (which also writes the tf32 planes a GEMM reads next)
+    for (int g = 0; g < n; ++g)
+        if (members[g].size() >= 2 || (members[g].size() == 1 && ok[g] && exchanges[g] && !order[g].origin->composite)) {
+            RowGroupPlan plan;
+            plan.members = members[g];
+            std::sort(plan.members.begin(), plan.members.end());
+            plans.push_back(plan);
+        }
+    return plans;
+}
+
 // Program::compile, session.rs:62-206.
-static std::unique_ptr<Program> compile(const std::vector<Var> &x, std::vector<Var> y, bool fusion, bool pattern, bool tc, bool softmax_in_gemm) {
+static std::unique_ptr<Program> compile(const std::vector<Var> &x, std::vector<Var> y, bool fusion, bool pattern, bool tc, bool softmax_in_gemm,
+                                        bool row_groups = false) {
     std::unique_ptr<Program> p(new Program());
     p->fusion = fusion;
     p->pattern = pattern;
@@ -398,7 +492,42 @@ static std::unique_ptr<Program> compile(const std::vector<Var> &x, std::vector<V
             state_order.push_back(node);
         }
     }
+    // row groups: states replaced by one generated kernel each
+    std::unordered_set<Origin *> grouped;
+    if (pattern && row_groups) {
+        std::unordered_map<Origin *, std::vector<Origin *>> readers;  // state -> states that read it
+        for (const Var &node : state_order)
+            for (const Var &in : states[node.key()]) readers[in.key()].push_back(node.key());
+        for (const RowGroupPlan &plan : plan_row_groups(state_order, states)) {
+            std::unordered_set<Origin *> inside;
+            for (int m : plan.members) inside.insert(state_order[m].key());
+            std::vector<Var> outs, leaves;
+            std::unordered_set<Origin *> seen;
+            for (int m : plan.members) {
+                const Var &v = state_order[m];
+                bool needed = yset.count(v.key()) != 0;
+                for (Origin *r : readers[v.key()])
+                    if (!inside.count(r)) needed = true;
+                if (needed) outs.push_back(v);
+                for (const Var &in : states[v.key()])
+                    if (!inside.count(in.key()) && seen.insert(in.key()).second) leaves.push_back(in);
+            }
+            if (outs.empty()) continue;
+            std::shared_ptr<RowProgram> row = row_program_build(leaves, outs, false, true);
+            if (!row) continue;  // e.g. an output that is only a view of another value: leave the states as they are
+            Routine r;
+            r.inputs = leaves;
+            r.output = outs[0];
+            r.row = row;
+            r.row_outputs = outs;
+            for (const Var &v : r.inputs)
+                if (v.is_op()) ++p->consumers[v.key()];
+            for (Origin *k : inside) grouped.insert(k);
+            for (const Var &o : outs) p->routines.emplace(o.key(), r);
+        }
+    }
     for (const Var &node : state_order) {
+        if (grouped.count(node.key())) continue;
         Routine r;
         r.inputs = states[node.key()];
         r.output = node;
@@ -416,10 +545,12 @@ static std::unique_ptr<Program> compile(const std::vector<Var> &x, std::vector<V
     }
     if (pattern) {
         std::unordered_set<Origin *> plane_states;
-        for (auto &kv : p->routines) mark_plane_readers(kv.second.root, tc, &plane_states);
+        for (auto &kv : p->routines)
+            if (!kv.second.row) mark_plane_readers(kv.second.root, tc, &plane_states);
         for (Origin *key : plane_states) {
             auto it = p->routines.find(key);
             if (it == p->routines.end()) continue;  // an input of the program: split on first use
+            if (it->second.row) continue;  // a row group writes fp32 only: its readers split on first use
             Node *root = skip_views(&it->second.root);
             if (!root->is_data && can_emit_planes(*root->op, tc)) root->emit_planes = true;
         }
@@ -507,10 +638,23 @@ static sage_status exec(Program &p, Context &ctx, Session &s) {
             continue;
         }
         Tensor out;
+        std::vector<Tensor> row_outs;
         for (;;) {
             auto t0 = std::chrono::steady_clock::now();
             SharedMemo memo;
-            sage_status st = run_node(f.root, ctx, s, temp, memo, &out);
+            sage_status st;
+            if (f.row) {
+                st = row_program_run(*f.row, ctx, [&](const Var &k, Tensor *t) {
+                    auto jt = temp.find(k.key());
+                    if (jt != temp.end()) {
+                        *t = jt->second;
+                        return true;
+                    }
+                    return s.get(k, t);
+                }, &row_outs);
+            } else {
+                st = run_node(f.root, ctx, s, temp, memo, &out);
+            }
             f.exec_time = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
             if (st == SAGE_OK) break;
             if (st != SAGE_ERR_OOM) return st;
@@ -541,8 +685,17 @@ static sage_status exec(Program &p, Context &ctx, Session &s) {
         }
         for (const Var &k : f.inputs) --lock[k.key()];
         pending.erase(v.key());
-        if (outputs.count(v.key())) s.data[v.key()] = std::make_pair(v, out);
-        else temp[v.key()] = out;
+        if (f.row) {  // every state of the group at once
+            for (size_t i = 0; i < f.row_outputs.size(); ++i) {
+                const Var &o = f.row_outputs[i];
+                if (outputs.count(o.key())) s.data[o.key()] = std::make_pair(o, row_outs[i]);
+                else temp[o.key()] = row_outs[i];
+            }
+        } else if (outputs.count(v.key())) {
+            s.data[v.key()] = std::make_pair(v, out);
+        } else {
+            temp[v.key()] = out;
+        }
         for (const Var &k : f.inputs) {
             auto it = remaining.find(k.key());
             if (it != remaining.end() && --it->second == 0) temp.erase(k.key());
@@ -597,7 +750,9 @@ sage_status Session::eval(const std::vector<Var> &targets) {
                     p->row = row;
                 }
             }
-            if (!p) p = compile(x, y, true, ctx_->opts().pattern_fusion != 0, ctx_->opts().gemm_backend != 1, (ctx_->opts().pattern_fusion & 2) != 0);
+            if (!p)
+                p = compile(x, y, true, ctx_->opts().pattern_fusion != 0, ctx_->opts().gemm_backend != 1, (ctx_->opts().pattern_fusion & 2) != 0,
+                            (ctx_->opts().pattern_fusion & 5) == 1 && row_programs_enabled());
         } catch (const ShapeError &e) {
             return ctx_->fail(SAGE_ERR_INVALID, e.msg);
         }
@@ -643,7 +798,12 @@ std::string Session::describe_last() const {
     std::sort(rs.begin(), rs.end(), [](const Routine *a, const Routine *b) {
         return a->output.t_order() != b->output.t_order() ? a->output.t_order() < b->output.t_order() : a->output.key() < b->output.key();
     });
+    std::unordered_set<const RowProgram *> shown;
     for (const Routine *r : rs) {
+        if (r->row) {
+            if (shown.insert(r->row.get()).second) out.append(row_program_describe(*r->row));
+            continue;
+        }
         describe_node(r->root, &out);
         out.push_back('\n');
     }

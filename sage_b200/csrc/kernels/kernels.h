@@ -129,6 +129,7 @@ struct TcGemm {
     TcAuxArg aux[3];
     std::string epilogue;    // C expression over x0 (the product) and x1..x3 (aux); empty = x0
     bool row_softmax = false;  // store softmax over each output row of the expression; needs n <= 256 (one tile per row)
+    int force_bn = 0;          // tile width chosen by the caller (64 / 128 / 192 / 256); 0 = the launcher's own choice
 };
 bool gemm_tc_shape_ok(long long m, long long n, long long k, long long batch);
 sage_status gemm_tc_run(Context &ctx, const TcGemm &g);

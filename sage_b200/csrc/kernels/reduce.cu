@@ -252,8 +252,8 @@ __global__ void __launch_bounds__(256) reduce_cols_kernel(const T *__restrict__ 
 }
 
 template <typename T>
-static sage_status launch_reduce_cols(Context &ctx, int kind, const T *x, long long rows, long long cols, long long pitch, T *y) {
-    const int compat = ctx.opts().ref_compat;
+static sage_status launch_reduce_cols(Context &ctx, int kind, const T *x, long long rows, long long cols, long long pitch, T *y, int compat_in) {
+    const int compat = compat_in < 0 ? ctx.opts().ref_compat : compat_in;
     const long long tiles = (cols + 31) / 32;
     long long chunks = (2LL * ctx.sm_count + tiles - 1) / tiles;
     chunks = std::max(1LL, std::min(chunks, rows / 64));
@@ -280,7 +280,7 @@ static sage_status launch_reduce_cols(Context &ctx, int kind, const T *x, long l
 }
 
 template <typename T>
-static sage_status launch_reduce(Context &ctx, int kind, const T *x, const Dims &outer_in, const Dims &inner_in, T *y) {
+static sage_status launch_reduce(Context &ctx, int kind, const T *x, const Dims &outer_in, const Dims &inner_in, T *y, int compat_in = -1) {
     RDims outer;
     outer.ndim = outer_in.ndim;
     for (int i = 0; i < outer_in.ndim; ++i) {
@@ -299,7 +299,51 @@ static sage_status launch_reduce(Context &ctx, int kind, const T *x, const Dims 
     const bool inner_contig = inner.str[inner.ndim - 1] == 1;
     // [rows, cols] -> [cols] (bias gradients, sums over the batch): the kept axis is the contiguous one
     if (outer_in.ndim == 1 && outer_in.str[0] == 1 && inner.ndim == 1 && inner.str[0] >= n_out && n_out >= 2 && n_in >= 64 && n_out <= (1LL << 31))
-        return launch_reduce_cols<T>(ctx, kind, x, n_in, n_out, inner.str[0], y);
+        return launch_reduce_cols<T>(ctx, kind, x, n_in, n_out, inner.str[0], y, compat_in);
+    // Few outputs, each over a long run (a sum over a whole tensor, the gradient of a scalar parameter): one
+    // CTA per output would leave the machine idle.  The run is cut into S equal chunks, a first launch
+    // reduces every (output, chunk) pair into scratch [n_out, S], a second one reduces the S partials; the
+    // order of combination is fixed.  The accumulator rule (start from 0) is applied by the second launch.
+    if (inner.ndim == 1 && n_out * 4 <= ctx.sm_count && n_in >= (1LL << 16) && outer.ndim < kMaxDims) {
+        long long want = std::min<long long>(4LL * ctx.sm_count / n_out, n_in / 4096), S = 0;
+        for (long long c = want; c >= want / 2 && c >= 2; --c)
+            if (n_in % c == 0) {
+                S = c;
+                break;
+            }
+        if (S >= 2) {
+            Block *scratch = ctx.dry() ? nullptr : ctx.allocator().alloc((size_t)(n_out * S) * sizeof(T));
+            if (scratch || ctx.dry()) {
+                const long long chunk = n_in / S;
+                Dims outer2 = outer_in, inner2;
+                if (outer2.ndim == 0) {
+                    outer2.ndim = 1;
+                    outer2.ext[0] = 1;
+                    outer2.str[0] = 0;
+                }
+                outer2.ext[outer2.ndim] = S;
+                outer2.str[outer2.ndim] = chunk * inner.str[0];
+                ++outer2.ndim;
+                inner2.ndim = 1;
+                inner2.ext[0] = chunk;
+                inner2.str[0] = inner.str[0];
+                T *partial = scratch ? reinterpret_cast<T *>(scratch->ptr) : nullptr;
+                sage_status st = launch_reduce<T>(ctx, kind, x, outer2, inner2, partial, 0);
+                if (!st) {
+                    Dims outer3, inner3;
+                    outer3.ndim = 1;
+                    outer3.ext[0] = n_out;
+                    outer3.str[0] = S;
+                    inner3.ndim = 1;
+                    inner3.ext[0] = S;
+                    inner3.str[0] = 1;
+                    st = launch_reduce<T>(ctx, kind, partial, outer3, inner3, y, compat_in);
+                }
+                if (scratch) ctx.allocator().free(scratch);
+                return st;
+            }
+        }
+    }
     int G = 1;
     if (inner_contig && n_in >= 64) G = (n_in >= 8192 || n_out < 2LL * ctx.sm_count) ? 256 : 32;
     // A column reduction with very few outputs would leave the GPU idle; a CTA per output is
@@ -307,7 +351,7 @@ static sage_status launch_reduce(Context &ctx, int kind, const T *x, const Dims 
     if (!inner_contig && n_out < 1024 && n_in >= 4096) G = 256;
     const int threads = 256;
     long long blocks = (n_out + (threads / G) - 1) / (threads / G);
-    const int compat = ctx.opts().ref_compat;
+    const int compat = compat_in < 0 ? ctx.opts().ref_compat : compat_in;
     ctx.note_launch(G == 1 ? "reduce_g1" : G == 32 ? "reduce_g32" : "reduce_g256");
     if (ctx.dry()) return SAGE_OK;
     bool vec = G > 1 && inner.ndim == 1 && inner_contig && n_in % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;

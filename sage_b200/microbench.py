@@ -53,7 +53,7 @@ def case_gemm(ctx, a):
     def go():
         ctx._ck(S.lib.sage_gemm_strided_batched(ctx.h, 0, 0, L(m), L(n), L(k), A.buf, L(0), L(k), L(m * k), B.buf, L(0), L(n), L(k * n),
                                                 C.buf, L(0), L(n), L(m * n), L(b)))
-    ms, prof = timed(ctx, go, a.reps, ["gemm"])
+    ms, prof = timed(ctx, go, a.reps, ["gemm", "reduce"])  # "reduce": the sum over K slices when the product is split over K
     split_ms = prof.get("split_tf32", (0, 0.0))[1] / a.reps
     hbm, bf16, src = peaks()
     tf = 2.0 * m * n * k * b / (ms * 1e-3) / 1e12

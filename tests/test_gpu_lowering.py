@@ -297,3 +297,53 @@ def test_row_softmax_in_the_gemm_epilogue(b, lq, lk, d):
     finally:
         lowered.close()
         plain.close()
+
+
+@pytest.mark.parametrize("n,l,e", [(4, 32, 256), (2, 7, 96), (3, 16, 1024)])
+def test_row_groups_inside_a_larger_program(n, l, e):
+    """LayerNorm's backward pass sits between GEMMs: its states (maps and row reductions over [n*l, e])
+    run as ONE generated kernel inside the larger program.  Gradients with the groups on (pattern_fusion
+    1) and off (5: kernel by kernel) agree to fp32 rounding, and both match float64."""
+    rng = np.random.default_rng(900 + e)
+    x = rng.standard_normal((n, l, e)).astype(np.float32)
+    w1 = (rng.standard_normal((e, e)) / np.sqrt(e)).astype(np.float32)
+    w2 = (rng.standard_normal((e, 8)) / np.sqrt(e)).astype(np.float32)
+    gamma, beta = np.float32([1.3]), np.float32([0.2])
+    outs = []
+    for fusion in (1, 5):
+        c = S.Context(0, pattern_fusion=fusion)
+        try:
+            xv, w1v, w2v, gv, bv = (c.var(a) for a in (x, w1, w2, gamma, beta))
+            h = S.layer_norm(S.matmul(xv, w1v) + xv, [2], gv, bv, 1e-5)
+            y = S.matmul(S.relu(h), w2v)
+            loss = (y * y).sum([0, 1, 2], False)
+            grads = S.grad(loss, [xv, w1v, w2v, gv, bv])
+            c.trace_begin()
+            c.eval(loss, *grads)
+            assert ("sage_row_program" in c.trace()) == (fusion == 1)
+            if fusion == 1:
+                assert "row_program[%dx%d" % (n * l, e) in c.describe()
+            outs.append([c.read(loss)] + [c.read(g) for g in grads])
+            assert c.status_word() == 0
+        finally:
+            c.close()
+    for a, b in zip(*outs):
+        assert gemm_err(a, b) <= 1e-4
+    # float64 reference of the same graph
+    X, W1, W2 = (a.astype(np.float64) for a in (x, w1, w2))
+    t = X @ W1 + X
+    mu, var = t.mean(-1, keepdims=True), (t * t).mean(-1, keepdims=True) - t.mean(-1, keepdims=True) ** 2
+    xh = (t - mu) / np.sqrt(var + 1e-5)
+    h = xh * 1.3 + 0.2
+    r = np.maximum(h, 0)
+    y = r @ W2
+    gy = 2 * y
+    gw2 = np.einsum("nle,nlo->eo", r, gy)
+    gh = (gy @ W2.T) * (h > 0)
+    ggamma, gbeta = (gh * xh).sum(), gh.sum()
+    gxh = gh * 1.3
+    gt = (gxh - gxh.mean(-1, keepdims=True) - xh * (gxh * xh).mean(-1, keepdims=True)) / np.sqrt(var + 1e-5)
+    gw1 = np.einsum("nle,nlo->eo", X, gt)
+    gx = gt @ W1.T + gt
+    for got, ref in zip(outs[0], [(y * y).sum().reshape(1), gx, gw1, gw2, np.array([ggamma]), np.array([gbeta])]):
+        assert gemm_err(got, ref.astype(np.float32)) <= 2e-4

@@ -173,7 +173,8 @@ def test_broadcast_and_strided_views(ctx):
 @pytest.mark.parametrize("shape,axes,preserve", [
     ((64, 1000), [1], True), ((64, 1000), [0], False), ((7, 9, 11, 5), [0, 2], False), ((7, 9, 11, 5), [3, 1], True),
     ((3, 20000), [1], False), ((5000, 3), [0], False), ((2, 3, 4), [0, 1, 2], False), ((1, 1), [1], True),
-    ((128, 7, 7, 64), [0, 1, 2], False), ((6272, 100), [0], True), ((40000, 33), [0], False), ((70, 512), [0], False)])
+    ((128, 7, 7, 64), [0, 1, 2], False), ((6272, 100), [0], True), ((40000, 33), [0], False), ((70, 512), [0], False),
+    ((2048, 1536), [0, 1], False), ((2, 300000), [1], True), ((3, 512, 256), [1, 2], False)])  # long runs, few outputs: two stages
 @pytest.mark.parametrize("kind", ["sum", "max", "min", "prod"])
 def test_reduce_vs_oracle(ctx, shape, axes, preserve, kind):
     rng = np.random.default_rng(10)

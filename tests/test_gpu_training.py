@@ -168,7 +168,7 @@ def test_update_refuses_a_parameter_that_is_not_data(ctx):
 
 def test_resnet18_training_step_vs_oracle(ctx):
     """examples/train.rs at a small batch: ResNet d18(1, 10) on 28 x 28 x 1 images, mean softmax cross
-    entropy, gradients of all 62 parameters, Adam."""
+    entropy, gradients of all 42 parameters, Adam."""
     rng = np.random.default_rng(4300)
     batch = 4
     model, rmodel = S.ResNet18(1, 10), R.resnet18(1, 10)

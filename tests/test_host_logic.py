@@ -322,3 +322,48 @@ def test_resnet18_plan():
     assert t.count("max_pool2d") == 1 and t.count("avg_pool2d") == 1
     assert len([k for k in t if k.startswith("gemm")]) == 21
     c.close()
+
+
+def test_training_step_plan(ctx):
+    """examples/train.rs on a planning context: one cached program evaluates the loss, the accuracy and the
+    gradients of all 42 parameters of ResNet d18(1, 10); Adam::update (src/optim.rs:134-177) is two launches
+    of the multi-parameter kernel (32 slots each); weight-gradient GEMMs with a long K are split over K."""
+    batch = 128
+    model = S.ResNet18(1, 10)
+    for p in model.params():
+        ctx.set(p, np.zeros(p.extents, np.float32))
+    xin, lin = S.Var.empty([batch, 28, 28, 1]), S.Var.empty([batch, 1], S.U32)
+    ctx.set(xin, np.zeros((batch, 28, 28, 1), np.float32))
+    ctx.set(lin, np.zeros((batch, 1), np.uint32))
+    logits = model.pass_(xin)
+    loss = S.softmax_cross_entropy(logits, lin).mean([0], False)
+    acc = S.accuracy(logits, lin)
+    assert acc.extents == (1,) and acc.dtype == S.F32
+    grads = S.grad_param(loss, model)
+    assert len(grads) == 42 and all(g.extents == p.extents for p, g in grads.items())
+    opt = S.Adam(1e-4)
+    opt.init(ctx)
+    ctx.eval(*grads.values(), loss, acc)
+    n = ctx.programs_compiled()
+    ctx.trace_begin()
+    opt.update(grads, ctx)
+    assert ctx.trace() == ["adam_update", "adam_update"]
+    ctx.clear()
+    ctx.trace_begin()
+    ctx.eval(*grads.values(), loss, acc)
+    assert ctx.programs_compiled() == n                       # the step's program is compiled once
+    t = ctx.trace()
+    assert t.count("reduce_cols") >= 21 and "col2im" in t    # bias gradients, input gradients of the convolutions
+    # gradients that the session has not evaluated are evaluated by update() itself (optim.rs:56-59)
+    ctx.clear()
+    ctx.trace_begin()
+    opt.update(grads, ctx)
+    assert ctx.trace()[-2:] == ["adam_update", "adam_update"] and len(ctx.trace()) > 100
+    # Sgd: one rule, no state; a parameter that is not a data variable is refused (optim.rs:52-54)
+    w = ctx.var(np.ones((4, 4), np.float32))
+    y = (w * w).sum([0, 1], False)
+    ctx.trace_begin()
+    S.Sgd(0.1).update({w: w.grad(y)}, ctx)
+    assert ctx.trace()[-1] == "sgd_update"
+    with pytest.raises(S.SageError):
+        S.Sgd(0.1).update({w * 2.0: w.grad(y)}, ctx)
