@@ -63,6 +63,20 @@ SG float sg_max(float a, float b) { return fmaxf(a, b); }
 SG int sg_max(int a, int b) { return a > b ? a : b; }
 SG uint sg_max(uint a, uint b) { return a > b ? a : b; }
 SG float sg_lit(uint bits) { return __uint_as_float(bits); }
+// hi = x rounded to tf32 (nearest, ties away), lo = x - hi; when the rounding overflows or x is inf / nan,
+// hi is the truncated value and lo what is left of a finite x (the rule of the GEMM's own split pass)
+SG void sg_split_tf32(float x, float *hi, float *lo) {
+  uint hb;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(x));
+  float hf = __uint_as_float(hb);
+  if ((hb & 0x7f800000u) == 0x7f800000u) {
+    hf = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+    *lo = ((__float_as_uint(x) & 0x7f800000u) != 0x7f800000u) ? x - hf : 0.f;
+  } else {
+    *lo = x - hf;
+  }
+  *hi = hf;
+}
 )";
 
 const char *map_prelude_text() { return kPrelude; }
@@ -71,7 +85,7 @@ static const char *ctype(int dt) { return dt == SAGE_F32 ? "float" : dt == SAGE_
 static const char *vtype(int dt) { return dt == SAGE_F32 ? "float4" : dt == SAGE_I32 ? "int4" : "uint4"; }
 
 sage_status map_plan(const std::string &expr, const std::vector<MapOperand> &in, int out_dtype, const void *y,
-                     int out_ndim, const long long *out_ext, MapPlan *plan, bool emit_source) {
+                     int out_ndim, const long long *out_ext, MapPlan *plan, bool emit_source, bool planes) {
     const int nin = (int)in.size();
     // ---- collapse axes
     long long ext[k::kMaxDims];
@@ -145,7 +159,7 @@ sage_status map_plan(const std::string &expr, const std::vector<MapOperand> &in,
     plan->vec = vec;
     const bool wide = n >= (1LL << 32);
     const char *it = wide ? "unsigned long long" : "unsigned int";
-    plan->signature = modes + ":" + std::to_string(vec) + ":" + std::to_string(nd) + (wide ? "w" : "n");
+    plan->signature = modes + ":" + std::to_string(vec) + ":" + std::to_string(nd) + (wide ? "w" : "n") + (planes ? "P" : "");
     if (!emit_source) return SAGE_OK;  // the caller already holds the kernel for this signature
 
     // ---- emit
@@ -158,7 +172,7 @@ sage_status map_plan(const std::string &expr, const std::vector<MapOperand> &in,
     s << ") { return (" << ctype(out_dtype) << ")(" << expr << "); }\n";
     s << "extern \"C\" __global__ void __launch_bounds__(256) sage_map(";
     for (int q = 0; q < nin; ++q) s << "const " << ctype(in[q].dtype) << " *__restrict__ x" << q << "_buf, ";
-    s << ctype(out_dtype) << " *__restrict__ y, const MapP p) {\n";
+    s << ctype(out_dtype) << " *__restrict__ y, const MapP p" << (planes ? ", float *__restrict__ hi, const long long plane" : "") << ") {\n";
     // launched as a programmatic dependent: wait for the kernel before this one before touching memory
     s << "  asm volatile(\"griddepcontrol.launch_dependents;\" ::: \"memory\");\n";
     s << "  asm volatile(\"griddepcontrol.wait;\" ::: \"memory\");\n";
@@ -190,9 +204,10 @@ sage_status map_plan(const std::string &expr, const std::vector<MapOperand> &in,
             else s << "i" << q;
             s << "];\n";
         }
-        s << "  y[g] = sage_expr(";
+        s << "  const " << ctype(out_dtype) << " r = sage_expr(";
         for (int q = 0; q < nin; ++q) s << (q ? ", " : "") << "x" << q;
-        s << ");\n";
+        s << ");\n  y[g] = r;\n";
+        if (planes) s << "  { float h, l; sg_split_tf32(r, &h, &l); hi[g] = h; hi[plane + g] = l; }\n";
     } else {
         for (int q = 0; q < nin; ++q) {
             const char *ct = ctype(in[q].dtype);
@@ -214,6 +229,9 @@ sage_status map_plan(const std::string &expr, const std::vector<MapOperand> &in,
             s << ");\n";
         }
         s << "  *reinterpret_cast<" << vtype(out_dtype) << " *>(y + g) = r;\n";
+        if (planes)
+            s << "  { float4 h, l; sg_split_tf32(r.x, &h.x, &l.x); sg_split_tf32(r.y, &h.y, &l.y); sg_split_tf32(r.z, &h.z, &l.z); "
+                 "sg_split_tf32(r.w, &h.w, &l.w);\n    *reinterpret_cast<float4 *>(hi + g) = h; *reinterpret_cast<float4 *>(hi + plane + g) = l; }\n";
     }
     s << "}\n";
     plan->source = s.str();
@@ -226,9 +244,10 @@ struct MapPHost {
 };
 
 sage_status map_launch(Context &ctx, const std::string &expr, const std::vector<MapOperand> &in, int out_dtype,
-                       void *y, int out_ndim, const long long *out_ext, MapCache *cache) {
+                       void *y, int out_ndim, const long long *out_ext, MapCache *cache, float *hi, long long plane) {
+    const bool planes = hi != nullptr && out_dtype == SAGE_F32;
     MapPlan plan;
-    sage_status st = map_plan(expr, in, out_dtype, y, out_ndim, out_ext, &plan, false);
+    sage_status st = map_plan(expr, in, out_dtype, y, out_ndim, out_ext, &plan, false, planes);
     if (st) return st;
     if (plan.n == 0) return SAGE_OK;
     Module *mod = nullptr;
@@ -237,7 +256,7 @@ sage_status map_launch(Context &ctx, const std::string &expr, const std::vector<
         if (it != cache->by_signature.end()) mod = it->second;
     }
     if (!mod) {
-        st = map_plan(expr, in, out_dtype, y, out_ndim, out_ext, &plan, true);  // first use: write the source
+        st = map_plan(expr, in, out_dtype, y, out_ndim, out_ext, &plan, true, planes);  // first use: write the source
         if (st) return st;
         st = ctx.module_get(plan.source, &mod);
         if (st) return st;
@@ -264,6 +283,10 @@ sage_status map_launch(Context &ctx, const std::string &expr, const std::vector<
     }
     params.push_back(&y);
     params.push_back(pb.data());
+    if (planes) {
+        params.push_back(&hi);
+        params.push_back(&plane);
+    }
     const long long chunks = (plan.n + plan.vec - 1) / plan.vec;
     const uint32_t grid[3] = {(uint32_t)((chunks + 255) / 256), 1, 1};
     const uint32_t block[3] = {256, 1, 1};

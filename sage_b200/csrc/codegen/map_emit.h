@@ -36,10 +36,13 @@ struct MapPlan {
 
 // `expr` is a C expression over x0..x{n-1}; helper functions come from the prelude
 // (sg_exp, sg_max, ...).  The output is contiguous with `out_ext`.
+// `planes`: the kernel also writes the tf32 hi / lo split of every (f32) result, laid out like y.
 sage_status map_plan(const std::string &expr, const std::vector<MapOperand> &in, int out_dtype, const void *y,
-                     int out_ndim, const long long *out_ext, MapPlan *plan, bool emit_source = true);
+                     int out_ndim, const long long *out_ext, MapPlan *plan, bool emit_source = true, bool planes = false);
 
+// `hi` (optional, f32 results only): hi plane of y's tf32 split, the lo plane `plane` floats further; a
+// tensor-core GEMM that reads y next then needs no split pass.
 sage_status map_launch(Context &ctx, const std::string &expr, const std::vector<MapOperand> &in, int out_dtype,
-                       void *y, int out_ndim, const long long *out_ext, MapCache *cache);
+                       void *y, int out_ndim, const long long *out_ext, MapCache *cache, float *hi = nullptr, long long plane = 0);
 
 }  // namespace sage

@@ -49,6 +49,8 @@ std::string map_expr_text(const MapExpr &e) {
     return "";
 }
 
+sage_status storage_planes_attach(Context &ctx, Storage &st);  // ops_gemm.cc
+
 struct MapOp : Operator {
     MapExpr expr;
     bool primitive = true;  // a single nullary/unary/binary/ternary op (differentiable); false once fused
@@ -61,8 +63,18 @@ struct MapOp : Operator {
     std::vector<Var> grad(const std::vector<Var> &x, const Var &y, const Var &gy) override;
 
     sage_status compute(const std::vector<Tensor> &x, Context &ctx, Tensor *y) override {
+        const bool emit = ctx.hint_emit_planes && out.dtype == SAGE_F32;
+        ctx.hint_emit_planes = ctx.hint_planes_only = false;
         sage_status st = Tensor::uninit(ctx, out, y);
         if (st) return st;
+        float *hi = nullptr;
+        long long plane = 0;
+        if (emit) {  // a tensor-core GEMM reads y next: the kernel writes its tf32 planes as well
+            st = storage_planes_attach(ctx, *y->data);
+            if (st) return st;
+            hi = y->data->split->planes.planes + y->desc.shape.offset;
+            plane = y->data->split->plane;
+        }
         if (text.empty()) text = map_expr_text(expr);
         std::vector<MapOperand> operands(x.size());
         for (size_t i = 0; i < x.size(); ++i) {
@@ -70,9 +82,14 @@ struct MapOp : Operator {
             operands[i].ptr = x[i].ptr();
             operands[i].view = x[i].dims();
         }
-        return map_launch(ctx, text, operands, out.dtype, y->ptr(), out.shape.rank(), out.shape.extents.data(), &cache);
+        return map_launch(ctx, text, operands, out.dtype, y->ptr(), out.shape.rank(), out.shape.extents.data(), &cache, hi, plane);
     }
 };
+
+bool map_op_emits_planes(const Operator &op) {
+    const MapOp *m = dynamic_cast<const MapOp *>(&op);
+    return m && m->out.dtype == SAGE_F32 && !m->in.empty();
+}
 
 const MapExpr *map_expr_of(const Operator &op) {
     const MapOp *m = dynamic_cast<const MapOp *>(&op);

@@ -221,6 +221,7 @@ void emit(RowProgram &p) {
     s << "#define RP_COL(e) ((((e) / RP_VEC) * RP_T + (int)threadIdx.x) * RP_VEC + (e) % RP_VEC)\n";
     s << "#define RP_OK(e) (RP_WHOLE || RP_COL(e) < RP_C)\n";
     s << "struct RowP { long long rows; int compat; int pad; const void *in[" << std::max<size_t>(1, p.in_val.size()) << "]; void *out["
+      << std::max<size_t>(1, p.out_val.size()) << "]; float *out_hi[" << std::max<size_t>(1, p.out_val.size()) << "]; long long out_plane["
       << std::max<size_t>(1, p.out_val.size()) << "]; };\n";
     s << R"(template <int K> SG float rp_apply(float a, float b) { return K == 0 ? a + b : K == 1 ? a * b : K == 2 ? fmaxf(a, b) : fminf(a, b); }
 template <int K> SG float rp_identity() { return K == 0 ? 0.f : K == 1 ? 1.f : K == 2 ? __int_as_float(0xff800000) : __int_as_float(0x7f800000); }
@@ -370,6 +371,20 @@ SG void rp_prefetch(const RowP &p, long long row, uint4 *stage);
                     s << "dst[c0] = " << name << "[j];\n";
                 }
                 s << "      }\n    }\n";
+                if (v.dtype == SAGE_F32) {  // the tf32 planes of this output, when a tensor-core GEMM reads it next
+                    s << "    if (p.out_hi[" << v.output << "]) {\n      float *hi = p.out_hi[" << v.output << "] + row * RP_C, *lo = hi + p.out_plane["
+                      << v.output << "];\n#pragma unroll\n      for (int j = 0; j < RP_NV; ++j) {\n"
+                      << "        const int c0 = (j * RP_T + (int)threadIdx.x) * RP_VEC;\n        if (RP_WHOLE || c0 < RP_C) {\n";
+                    if (p.vec == 4) {
+                        s << "          float4 h, l;\n";
+                        for (int q = 0; q < 4; ++q)
+                            s << "          sg_split_tf32(" << name << "[4 * j + " << q << "], &h." << comp[q] << ", &l." << comp[q] << ");\n";
+                        s << "          *reinterpret_cast<float4 *>(hi + c0) = h;\n          *reinterpret_cast<float4 *>(lo + c0) = l;\n";
+                    } else {
+                        s << "          float h, l;\n          sg_split_tf32(" << name << "[j], &h, &l);\n          hi[c0] = h;\n          lo[c0] = l;\n";
+                    }
+                    s << "        }\n      }\n    }\n";
+                }
             } else {
                 s << "    if (threadIdx.x == 0) ((" << T << " *)p.out[" << v.output << "])[row] = " << name << ";\n";
             }
@@ -475,7 +490,10 @@ sage_status row_program_exec(RowProgram &p, Context &ctx, Session &s) {
     return SAGE_OK;
 }
 
-sage_status row_program_run(RowProgram &p, Context &ctx, const std::function<bool(const Var &, Tensor *)> &fetch, std::vector<Tensor> *outs_) {
+sage_status storage_planes_attach(Context &ctx, Storage &st);  // ops_gemm.cc
+
+sage_status row_program_run(RowProgram &p, Context &ctx, const std::function<bool(const Var &, Tensor *)> &fetch, std::vector<Tensor> *outs_,
+                            const std::vector<char> *planes) {
     if (p.source.empty()) return ctx.fail(SAGE_ERR_INVALID, "internal: row program was built for analysis only");
     if (p.owner != &ctx) {
         sage_status st = ctx.module_get(p.source, &p.module);
@@ -484,7 +502,8 @@ sage_status row_program_run(RowProgram &p, Context &ctx, const std::function<boo
         p.resident = ctx.blocks_per_sm(p.module, "sage_row_program", p.threads, p.stage_bytes);
     }
     std::vector<Tensor> keep;
-    std::vector<uint64_t> pb(2 + std::max<size_t>(1, p.in_val.size()) + std::max<size_t>(1, p.out_val.size()), 0);
+    const size_t nin = std::max<size_t>(1, p.in_val.size()), nout = std::max<size_t>(1, p.out_val.size());
+    std::vector<uint64_t> pb(2 + nin + 3 * nout, 0);  // rows, compat, in[], out[], out_hi[], out_plane[]
     pb[0] = (uint64_t)p.rows;
     pb[1] = (uint64_t)(ctx.opts().ref_compat ? 1 : 0);
     for (size_t i = 0; i < p.in_val.size(); ++i) {
@@ -518,7 +537,14 @@ sage_status row_program_run(RowProgram &p, Context &ctx, const std::function<boo
     for (size_t i = 0; i < p.out_val.size(); ++i) {
         sage_status st = Tensor::uninit(ctx, p.vals[p.out_val[i]].var.desc, &outs[i]);
         if (st) return st;
-        pb[2 + std::max<size_t>(1, p.in_val.size()) + i] = (uint64_t)reinterpret_cast<uintptr_t>(outs[i].ptr());
+        pb[2 + nin + i] = (uint64_t)reinterpret_cast<uintptr_t>(outs[i].ptr());
+        const Val &ov = p.vals[p.out_val[i]];
+        if (planes && i < planes->size() && (*planes)[i] && ov.cls == Full && ov.dtype == SAGE_F32) {
+            st = storage_planes_attach(ctx, *outs[i].data);
+            if (st) return st;
+            pb[2 + nin + nout + i] = (uint64_t)reinterpret_cast<uintptr_t>(outs[i].data->split->planes.planes + outs[i].desc.shape.offset);
+            pb[2 + nin + 2 * nout + i] = (uint64_t)outs[i].data->split->plane;
+        }
     }
     const long long resident = (long long)ctx.sm_count * p.resident;  // persistent: as many blocks as fit at once
     const uint32_t grid[3] = {(uint32_t)std::min<long long>(p.rows, resident), 1, 1};

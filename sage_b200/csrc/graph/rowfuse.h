@@ -29,7 +29,9 @@ std::shared_ptr<RowProgram> row_program_build(const std::vector<Var> &evaluated,
 // Allocates the targets, launches the kernel, stores the results in `s.data`.
 sage_status row_program_exec(RowProgram &p, Context &ctx, Session &s);
 // The same with the caller's own lookup of the (non-data) inputs; `outs` are the targets in order.
-sage_status row_program_run(RowProgram &p, Context &ctx, const std::function<bool(const Var &, Tensor *)> &fetch, std::vector<Tensor> *outs);
+// `planes` (optional, one flag per target): also write the tf32 hi / lo planes of that (f32, full-size) target.
+sage_status row_program_run(RowProgram &p, Context &ctx, const std::function<bool(const Var &, Tensor *)> &fetch, std::vector<Tensor> *outs,
+                            const std::vector<char> *planes = nullptr);
 void row_program_space(const RowProgram &p, long long *rows, long long *cols);
 std::vector<Var> row_program_inputs(const RowProgram &p);
 int row_program_exchanges(const RowProgram &p);  // reductions + gathers + scatters in the program

@@ -71,6 +71,7 @@ struct Routine {
     // same routine is registered under every state in `row_outputs`; running it once yields them all.
     std::shared_ptr<RowProgram> row;
     std::vector<Var> row_outputs;
+    std::shared_ptr<std::vector<char>> row_emit_shared;  // per output: a tensor-core GEMM reads it, write its tf32 planes too
 };
 
 struct Program {
@@ -246,8 +247,9 @@ static Node *skip_views(Node *p) {
         else return p;
     }
 }
+bool map_op_emits_planes(const Operator &op);
 static bool can_emit_planes(const Operator &op, bool tc) {
-    return gemm_runs_on_tc(op, tc) || row_op_emits_planes(op) || is_grouped_gemm_op(op);
+    return gemm_runs_on_tc(op, tc) || row_op_emits_planes(op) || is_grouped_gemm_op(op) || (tc && map_op_emits_planes(op));
 }
 
 // GEMMs of one routine that multiply the same A (same leaf, same view) by different weights, with
@@ -520,6 +522,7 @@ static std::unique_ptr<Program> compile(const std::vector<Var> &x, std::vector<V
             r.output = outs[0];
             r.row = row;
             r.row_outputs = outs;
+            r.row_emit_shared = std::make_shared<std::vector<char>>(outs.size(), 0);
             for (const Var &v : r.inputs)
                 if (v.is_op()) ++p->consumers[v.key()];
             for (Origin *k : inside) grouped.insert(k);
@@ -548,9 +551,20 @@ static std::unique_ptr<Program> compile(const std::vector<Var> &x, std::vector<V
         for (auto &kv : p->routines)
             if (!kv.second.row) mark_plane_readers(kv.second.root, tc, &plane_states);
         for (Origin *key : plane_states) {
+            // A state that is only a view of another state (reshape(state)) shares its storage, and planes
+            // belong to the storage: ask the state that really produces the values.
             auto it = p->routines.find(key);
+            for (int hops = 0; it != p->routines.end() && !it->second.row && hops < 8; ++hops) {
+                Node *root = skip_views(&it->second.root);
+                if (!root->is_data || !root->var.is_op()) break;
+                it = p->routines.find(root->var.key());
+            }
             if (it == p->routines.end()) continue;  // an input of the program: split on first use
-            if (it->second.row) continue;  // a row group writes fp32 only: its readers split on first use
+            if (it->second.row) {                   // a row group: the generated kernel writes the planes of that output
+                for (size_t i = 0; i < it->second.row_outputs.size(); ++i)
+                    if (it->second.row_outputs[i].key() == it->first) (*it->second.row_emit_shared)[i] = 1;
+                continue;
+            }
             Node *root = skip_views(&it->second.root);
             if (!root->is_data && can_emit_planes(*root->op, tc)) root->emit_planes = true;
         }
@@ -651,7 +665,7 @@ static sage_status exec(Program &p, Context &ctx, Session &s) {
                         return true;
                     }
                     return s.get(k, t);
-                }, &row_outs);
+                }, &row_outs, f.row_emit_shared.get());
             } else {
                 st = run_node(f.root, ctx, s, temp, memo, &out);
             }
