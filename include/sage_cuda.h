@@ -124,6 +124,11 @@ typedef struct {
 sage_status sage_mem_stats(sage_ctx *ctx, sage_mem_stats_t *stats);
 /* Pool::release_cached_blocks — memory.rs:454-474: return every fully-free segment to the device. */
 sage_status sage_release_cached(sage_ctx *ctx);
+/* Pool::garbage_collect — memory.rs:410-452: when 80 % of the capacity is in use, whole cached segments go
+ * back to the device, oldest first (age = searches of the pool a block sat through), until 20 % of the
+ * capacity is reclaimed.  Runs by itself inside sage_alloc when no cached block fits; this entry point runs
+ * it on demand.  `reclaimed` = bytes freed by this call; `runs_total` / `reclaimed_total` = since creation. */
+sage_status sage_garbage_collect(sage_ctx *ctx, uint64_t *reclaimed, uint64_t *runs_total, uint64_t *reclaimed_total);
 
 /* Buffer::write / Buffer::read (blocking) — src/session/device.rs:111-147 */
 sage_status sage_upload(sage_ctx *ctx, sage_buf *dst, size_t dst_offset, const void *src, size_t bytes);

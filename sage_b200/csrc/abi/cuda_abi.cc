@@ -155,6 +155,15 @@ sage_status sage_release_cached(sage_ctx *ctx) {
     C.allocator().release_cached();
     return SAGE_OK;
 }
+sage_status sage_garbage_collect(sage_ctx *ctx, uint64_t *reclaimed, uint64_t *runs_total, uint64_t *reclaimed_total) {
+    if (!ctx || !ctx->impl) return SAGE_ERR_INVALID;
+    Allocator &a = ctx->impl->allocator();
+    const uint64_t r = a.garbage_collect();
+    if (reclaimed) *reclaimed = r;
+    if (runs_total) *runs_total = a.gc_runs;
+    if (reclaimed_total) *reclaimed_total = a.gc_reclaimed;
+    return SAGE_OK;
+}
 
 sage_status sage_upload(sage_ctx *ctx, sage_buf *dst, size_t off, const void *src, size_t bytes) {
     CTX_OR_FAIL(ctx);

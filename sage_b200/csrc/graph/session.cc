@@ -10,6 +10,8 @@
 //     fusion is on, the composite's inputs take the place of the decomposed sub-graph;
 //   * an intermediate is released as soon as its last consumer routine has run (the reference keeps
 //     every intermediate until exec returns unless it runs out of memory).
+#include <cuda_runtime.h>
+
 #include <chrono>
 #include <cstdlib>
 
@@ -62,11 +64,33 @@ static bool row_programs_enabled() {
     return on;
 }
 
+// Device time of a routine's first execution, taken with a pair of events on the context's stream and
+// read once the second event has completed.  The reference measures the host time of the enqueue
+// (session.rs:667-668), which says little about an asynchronous device.
+struct RoutineTimer {
+    cudaEvent_t ev[2] = {nullptr, nullptr};
+    ~RoutineTimer() {
+        for (cudaEvent_t e : ev)
+            if (e) cudaEventDestroy(e);
+    }
+};
+
 struct Routine {
     std::vector<Var> inputs;
     Var output;
     Node root;
-    double exec_time = 0.0;
+    double exec_time = 0.0;  // microseconds on the device (host enqueue time on a planning context)
+    std::shared_ptr<RoutineTimer> timer;
+    bool timed = false;
+    // Reads the timer if the device has got that far; true when exec_time is final.
+    bool resolve_time() {
+        if (!timer) return true;
+        if (cudaEventQuery(timer->ev[1]) != cudaSuccess) return false;
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, timer->ev[0], timer->ev[1]) == cudaSuccess) exec_time = 1e3 * (double)ms;
+        timer.reset();
+        return true;
+    }
     // A row group (rowfuse.h): several states of one [R, C] space computed by one generated kernel.  The
     // same routine is registered under every state in `row_outputs`; running it once yields them all.
     std::shared_ptr<RowProgram> row;
@@ -624,6 +648,7 @@ static sage_status run_node(const Node &n, Context &ctx, Session &s, const std::
 
 // Program::exec, session.rs:208-468.
 static sage_status exec(Program &p, Context &ctx, Session &s) {
+    for (auto &kv : p.routines) kv.second.resolve_time();  // timers of an earlier run whose events have completed
     std::unordered_map<Origin *, Tensor> temp;
     std::unordered_map<Origin *, int> remaining = p.consumers;
     std::unordered_map<Origin *, int> lock;        // how many pending routines need each state
@@ -655,6 +680,13 @@ static sage_status exec(Program &p, Context &ctx, Session &s) {
         std::vector<Tensor> row_outs;
         for (;;) {
             auto t0 = std::chrono::steady_clock::now();
+            std::shared_ptr<RoutineTimer> timer;
+            if (!f.timed && !ctx.dry()) {
+                timer = std::make_shared<RoutineTimer>();
+                if (cudaEventCreate(&timer->ev[0]) != cudaSuccess || cudaEventCreate(&timer->ev[1]) != cudaSuccess ||
+                    cudaEventRecord(timer->ev[0], ctx.stream()) != cudaSuccess)
+                    timer.reset();
+            }
             SharedMemo memo;
             sage_status st;
             if (f.row) {
@@ -669,7 +701,12 @@ static sage_status exec(Program &p, Context &ctx, Session &s) {
             } else {
                 st = run_node(f.root, ctx, s, temp, memo, &out);
             }
-            f.exec_time = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+            if (timer && st == SAGE_OK && cudaEventRecord(timer->ev[1], ctx.stream()) == cudaSuccess) {
+                f.timer = timer;
+                f.timed = true;
+            } else if (!f.timed) {
+                f.exec_time = 1e6 * std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+            }
             if (st == SAGE_OK) break;
             if (st != SAGE_ERR_OOM) return st;
             // Out of memory: drop the intermediates that are cheapest to recompute per byte
@@ -684,6 +721,8 @@ static sage_status exec(Program &p, Context &ctx, Session &s) {
                     if (lk != lock.end() && lk->second > 0) continue;
                     auto r2 = p.routines.find(kv.first);
                     if (r2 == p.routines.end()) continue;
+                    r2->second.resolve_time();
+                    // cost of recomputing per element kept (session.rs:301-302), with the device time in microseconds
                     const double tpm = (r2->second.exec_time + 1.0) / ((double)r2->second.output.size() + 1.0);
                     if (!best || tpm < best_tpm) {
                         best = kv.first;

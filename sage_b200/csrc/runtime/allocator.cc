@@ -41,7 +41,13 @@ size_t Allocator::round_size(size_t bytes) {
 // Pool::get_free_block — memory.rs:283-334: best fit among blocks that are large enough,
 // never carving a small request out of a >= 40 MiB block, nor a huge request out of a block
 // more than 20 MiB larger; split off the remainder when it is worth keeping.
+void Allocator::enter(FreeSet &pool, Block *b) {
+    b->entered = searches_[&pool == &small_free_ ? 1 : 0];  // age 0: ages count the searches a block sits through
+    pool.insert(b);
+}
+
 Block *Allocator::find_free(FreeSet &pool, size_t size) {
+    ++searches_[&pool == &small_free_ ? 1 : 0];  // every block of the pool grows one search older (memory.rs:287)
     Block key;
     key.size = size;
     key.ptr = nullptr;
@@ -64,7 +70,7 @@ Block *Allocator::find_free(FreeSet &pool, size_t size) {
             if (b->next) b->next->prev = r;
             b->next = r;
             b->size = size;
-            pool.insert(r);
+            enter(pool, r);
         }
         b->free_ = false;
         return b;
@@ -97,7 +103,7 @@ bool Allocator::grow(size_t size, bool small) {
     b->size = seg;
     b->small = small;
     b->segment = p;
-    (small ? small_free_ : large_free_).insert(b);
+    enter(small ? small_free_ : large_free_, b);
     return true;
 }
 
@@ -132,9 +138,13 @@ Block *Allocator::alloc(size_t bytes) {
     FreeSet &pool = small ? small_free_ : large_free_;
     Block *b = find_free(pool, size);
     if (!b) {
+        garbage_collect();  // memory.rs:339: old cached segments go first, when the pool is nearly full
         if (!grow(size, small)) {
-            release_cached();  // memory.rs:344-349: give cached segments back, then retry once
-            if (!grow(size, small)) return nullptr;
+            release_largest(size);  // memory.rs:344-349: give cached segments back, largest first, then retry
+            if (!grow(size, small)) {
+                release_cached();  // (not in the reference) everything that is cached, small pool included
+                if (!grow(size, small)) return nullptr;
+            }
         }
         b = find_free(pool, size);
         if (!b) return nullptr;
@@ -173,10 +183,74 @@ void Allocator::free(Block *b) {
         if (n->next) n->next->prev = b;
         delete n;
     }
-    pool.insert(b);
+    enter(pool, b);
 }
 
-// Pool::release_cached_blocks — memory.rs:454-474 (here: every unsplit free segment).
+// Pool::garbage_collect — memory.rs:410-452.  Runs only when 80 % of the capacity is in use; frees whole
+// cached segments of the large pool, oldest first (age >= the average age of what is left), until 20 % of
+// the capacity has been given back or nothing old enough remains.
+size_t Allocator::garbage_collect() {
+    const uint64_t threshold = (uint64_t)((double)capacity_ * 0.8);  // GC_THRESHOLD
+    if (used_ < threshold) return 0;
+    const uint64_t target = capacity_ - threshold;
+    const uint64_t now = searches_[0];
+    uint64_t total_age = 0, freeable = 0;
+    for (Block *b : large_free_)
+        if (!b->prev && !b->next) {
+            total_age += now - b->entered;
+            ++freeable;
+        }
+    size_t reclaimed = 0;
+    bool freed = true;
+    while (reclaimed < target && freed && freeable > 0) {
+        const uint64_t age_threshold = total_age / freeable;
+        freed = false;
+        for (auto it = large_free_.begin(); it != large_free_.end();) {
+            Block *b = *it;
+            if (!b->prev && !b->next && now - b->entered >= age_threshold) {
+                it = large_free_.erase(it);
+                reclaimed += b->size;
+                total_age -= now - b->entered;
+                --freeable;
+                total_ -= b->size;
+                mem_->release(b->segment);
+                delete b;
+                freed = true;
+            } else {
+                ++it;
+            }
+        }
+    }
+    if (reclaimed) {
+        ++gc_runs;
+        gc_reclaimed += reclaimed;
+    }
+    return reclaimed;
+}
+
+// Pool::release_cached_blocks — memory.rs:454-474: whole cached segments of the large pool, largest first,
+// until max(size, SPLIT_LIM) bytes have gone back to the device.
+size_t Allocator::release_largest(size_t size) {
+    size_t released = 0;
+    const size_t want = std::max(size, kSplitLim);
+    while (released < want) {
+        Block *best = nullptr;
+        for (auto it = large_free_.rbegin(); it != large_free_.rend(); ++it)
+            if (!(*it)->prev && !(*it)->next) {
+                best = *it;  // the set is ordered by size: the first whole segment from the top is the largest
+                break;
+            }
+        if (!best) break;
+        large_free_.erase(best);
+        released += best->size;
+        total_ -= best->size;
+        mem_->release(best->segment);
+        delete best;
+    }
+    return released;
+}
+
+// Every unsplit free segment of both pools (sage_release_cached, and the last resort of alloc).
 void Allocator::release_cached() {
     for (FreeSet *pool : {&small_free_, &large_free_}) {
         for (auto it = pool->begin(); it != pool->end();) {

@@ -40,6 +40,7 @@ struct Block {
     bool small = false;
     Block *prev = nullptr, *next = nullptr;  // neighbours inside the same segment
     void *segment = nullptr;
+    uint64_t entered = 0;  // the pool's search count when the block last entered its free list (Age, memory.rs:756-786)
 };
 
 class Allocator {
@@ -59,6 +60,9 @@ public:
     Block *alloc(size_t bytes);
     void free(Block *b);
     void release_cached();
+    // Pool::garbage_collect — memory.rs:410-452; returns the bytes given back to the device.
+    size_t garbage_collect();
+    uint64_t gc_runs = 0, gc_reclaimed = 0;  // collections that freed something, bytes they freed
 
     uint64_t capacity() const { return capacity_; }
     uint64_t mem_total() const { return total_; }
@@ -76,6 +80,9 @@ private:
     typedef std::set<Block *, Cmp> FreeSet;
     Block *find_free(FreeSet &pool, size_t size);
     bool grow(size_t size, bool small);
+    size_t release_largest(size_t size);
+    void enter(FreeSet &pool, Block *b);
+    uint64_t searches_[2] = {0, 0};  // get_free_block calls per pool (large, small): the clock block ages are read against
     static size_t round_size(size_t bytes);
 
     std::unique_ptr<DeviceMem> mem_;

@@ -151,7 +151,7 @@ def case_train_resnet(ctx, a):
     step()
     prof = ctx.profile_end()
     total = sum(t for n, t in prof.values())
-    top = sorted(prof.items(), key=lambda kv: -kv[1][1])[:8]
+    top = sorted(prof.items(), key=lambda kv: -kv[1][1])[:a.top]
     return {"case": "train_resnet18_mnist_shape", "batch": batch, "ms_per_step": ms, "images_per_s": batch / (ms * 1e-3),
             "launches_per_step": sum(n for n, t in prof.values()), "loss_after_3_steps": first_loss, "loss_now": last["loss"],
             "kernel_ms": {k: [n, round(t, 4)] for k, (n, t) in top}, "profiled_step_ms": total}
@@ -198,7 +198,7 @@ def case_train_bert(ctx, a):
     ctx.profile_begin()
     step()
     prof = ctx.profile_end()
-    top = sorted(prof.items(), key=lambda kv: -kv[1][1])[:10]
+    top = sorted(prof.items(), key=lambda kv: -kv[1][1])[:a.top]
     return {"case": "train_bert_base", "batch": batch, "seq": seq, "ms_per_step": ms, "sequences_per_s": batch / (ms * 1e-3),
             "launches_per_step": sum(n for n, t in prof.values()), "loss_after_3_steps": first_loss, "loss_now": last["loss"],
             "kernel_ms": {k: [n, round(t, 4)] for k, (n, t) in top}, "profiled_step_ms": sum(t for n, t in prof.values()),
@@ -246,6 +246,8 @@ def main():
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=4096)
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--top", type=int, default=10, help="training cases: how many kernels of the profiled step to list "
+                    "(SAGE_VERBOSE_NAMES=1 gives one name per GEMM shape and map expression)")
     ap.add_argument("--device", type=int, default=0)
     a = ap.parse_args()
     if a.case == "tf32_peak":

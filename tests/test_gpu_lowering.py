@@ -347,3 +347,38 @@ def test_row_groups_inside_a_larger_program(n, l, e):
     gx = gt @ W1.T + gt
     for got, ref in zip(outs[0], [(y * y).sum().reshape(1), gx, gw1, gw2, np.array([ggamma]), np.array([gbeta])]):
         assert gemm_err(got, ref.astype(np.float32)) <= 2e-4
+
+
+def test_out_of_memory_evicts_recomputes_and_gives_the_same_values():
+    """Program::exec's out-of-memory path (src/session.rs:259-331) on the device: with a tight capacity the
+    evaluator drops the intermediates that are cheapest to recompute per element (device time from events)
+    and rebuilds them on demand; the result equals, bit for bit, the one computed with room to spare."""
+    n = 1 << 20  # 4 MiB tensors
+    x = np.random.default_rng(77).standard_normal(n).astype(np.float32) * 1e-3
+    outs, launches = [], []
+    for cap in (0, 44 << 20):
+        c = S.Context(0, **({"mem_capacity_bytes": cap} if cap else {}))
+        try:
+            xv = c.var(x)
+            a = [xv * float(i + 2) + 1.0 for i in range(12)]
+            s = [v.sum([0], True) for v in a]
+            z = s[0]
+            for v in s[1:]:
+                z = z + v
+            t = [(v * z.expand([n])).sum([0], True) for v in a]
+            out = s[0] * 0.0
+            for v, w in zip(t, s):
+                out = out + v + v * 2.0 + w
+            c.trace_begin()
+            for _ in range(2):   # the second pass uses the device times measured in the first
+                c.clear()
+                c.eval(out)
+            outs.append(c.read(out))
+            launches.append(len(c.trace()))
+            if cap:
+                assert c.mem_stats()["mem_peak"] <= cap
+            assert c.status_word() == 0
+        finally:
+            c.close()
+    assert np.array_equal(outs[0], outs[1]) and np.isfinite(outs[0]).all()
+    assert launches[1] > launches[0]   # states were evicted and computed again

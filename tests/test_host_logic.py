@@ -367,3 +367,43 @@ def test_training_step_plan(ctx):
     assert ctx.trace()[-1] == "sgd_update"
     with pytest.raises(S.SageError):
         S.Sgd(0.1).update({w * 2.0: w.grad(y)}, ctx)
+
+
+def test_allocator_garbage_collects_old_cached_segments():
+    """Pool::garbage_collect (src/session/memory.rs:410-452): nothing happens below 80 % use; above it, whole
+    cached segments of the large pool go back to the device, oldest first (age = how many searches of the pool
+    a block sat through), until 20 % of the capacity is reclaimed.  Pool::alloc runs it when no cached block
+    fits (:336-341), before it tries to grow."""
+    MiB = 1 << 20
+    c = S.Context(-1, mem_capacity_bytes=250 * MiB)  # threshold 200 MiB in use, target 50 MiB
+
+    def gc():
+        r, runs, total = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
+        assert S.lib.sage_garbage_collect(c.h, ctypes.byref(r), ctypes.byref(runs), ctypes.byref(total)) == 0
+        return r.value, runs.value, total.value
+    old = c.alloc(12 * MiB)
+    c.free(old)                                     # cached; every later search of the large pool ages it
+    held = [c.alloc(20 * MiB) for _ in range(3)]    # 3 searches
+    young = [c.alloc(14 * MiB), c.alloc(16 * MiB)]
+    for b in young:
+        c.free(b)                                   # two younger cached segments
+    s = c.mem_stats()
+    assert s["mem_total"] == (12 + 60 + 14 + 16) * MiB and s["mem_used"] == 60 * MiB
+    assert gc() == (0, 0, 0)                        # 60 of 250 MiB in use: below the threshold
+    held += [c.alloc(20 * MiB) for _ in range(7)]   # none of the cached segments fits: the pool grows to 242 MiB
+    assert c.mem_stats()["mem_used"] == 200 * MiB and c.mem_stats()["mem_total"] == 242 * MiB
+    r, runs, total = gc()
+    # 80 % in use.  Round 1 frees what is at least of average age (the old 12 MiB segment), round 2 the two
+    # younger ones; 42 < 50 MiB, but nothing is left
+    assert r == (12 + 14 + 16) * MiB and runs == 1 and total == r
+    assert c.mem_stats()["mem_total"] == 200 * MiB
+    # inside alloc: when no cached block fits, old cached segments are collected before the pool grows
+    c.free(held.pop())                              # a whole 20 MiB segment is cached, 180 MiB in use
+    held.append(c.alloc(30 * MiB))                  # does not fit it; below the threshold: no collection, grows
+    assert c.mem_stats()["mem_total"] == 230 * MiB
+    held.append(c.alloc(21 * MiB))                  # 210 MiB in use: the cached 20 MiB go back, then 22 MiB are added
+    assert c.mem_stats()["mem_total"] == 232 * MiB
+    assert gc() == (0, 2, total + 20 * MiB)         # that collection ran inside alloc; nothing is left to collect
+    for b in held:
+        c.free(b)
+    c.close()
