@@ -241,6 +241,11 @@ sage_status sage_col2im(sage_ctx *ctx, const sage_tensor *x, const sage_window *
 /* max_pool_2d / avg_pool_2d = im2col + reduce over [KH,KW] — src/ops/conv.rs:143-165, without
  * materialising the column tensor.  is_max: 1 max, 0 mean.  Padded taps count as zeros. */
 sage_status sage_pool2d(sage_ctx *ctx, int32_t is_max, const sage_tensor *x, const sage_window *w, const sage_tensor *y);
+/* conv_2d — src/ops/conv.rs:61-96: x [N,H,W,C] and filter [KH,KW,C,OC] (any strides) -> y [N,OH,OW,OC]
+ * contiguous, OH = (H + 2 pad - dil (KH - 1) - 1) / stride + 1 (:47-59); `w.ker` is ignored (the filter's
+ * extents give it).  The reference materialises im2col(x) and calls its GEMM; here the product runs as an
+ * implicit GEMM on the tensor cores when C % 32 == 0, otherwise the GEMM builds its column planes on the fly. */
+sage_status sage_conv2d_nhwc(sage_ctx *ctx, const sage_tensor *x, const sage_tensor *filter, const sage_window *w, const sage_tensor *y);
 
 /* ------------------------------------------------------------------ multi-GPU (no reference counterpart:
  * the reference has no multi-device code).  Batch shards are independent; the only exchange

@@ -293,6 +293,49 @@ sage_status sage_op_layer_norm(const sage_var *x, int32_t naxes, const int64_t *
 
 sage_status sage_op_accuracy(const sage_var *logits, const sage_var *labels, sage_var **out) { OP(ops::accuracy(logits->v, labels->v)); }
 
+// conv_2d over caller-owned buffers (declared in sage_cuda.h; lives here because the lowering to an implicit
+// GEMM is part of the graph evaluator).  The operands are wrapped as tensors that do not own their memory.
+static Tensor borrow(sage_ctx *ctx, const sage_tensor *t) {
+    Tensor out;
+    Array e(t->extents, t->extents + t->ndim), st(t->strides, t->strides + t->ndim);
+    out.desc = TensorDesc(Shape(e, st, t->offset), t->dtype);
+    auto s = std::make_shared<Storage>();
+    s->ctx = ctx->impl;
+    s->dev = t->buf->ptr;
+    s->bytes = t->buf->size;
+    out.data = s;  // no allocator, no block: nothing is freed when the handle drops
+    return out;
+}
+
+sage_status sage_conv2d_nhwc(sage_ctx *ctx, const sage_tensor *x, const sage_tensor *filter, const sage_window *w, const sage_tensor *y) {
+    if (!ctx || !ctx->impl || !x || !filter || !w || !y || !x->buf || !filter->buf || !y->buf) return SAGE_ERR_INVALID;
+    Context &C = *ctx->impl;
+    sage_status st = guarded([&]() -> sage_status {
+        if (x->ndim != 4 || filter->ndim != 4 || y->ndim != 4) shape_fail("conv2d: x, filter and y must have rank 4");
+        if (x->dtype != SAGE_F32 || filter->dtype != SAGE_F32 || y->dtype != SAGE_F32) shape_fail("conv2d: f32 only");
+        Session session(&C);
+        Var xv = Var::from_tensor(borrow(ctx, x)), fv = Var::from_tensor(borrow(ctx, filter));
+        Var out = ops::conv_2d(xv, fv, pr(w->stride), pr(w->pad), pr(w->dil));
+        Array ye(y->extents, y->extents + 4);
+        if (out.extents() != ye) shape_fail("conv2d: y does not have the extents of the result");
+        long long run = 1;
+        for (int i = 3; i >= 0; --i) {
+            if (y->extents[i] != 1 && y->strides[i] != run) shape_fail("conv2d: y must be contiguous");
+            run *= y->extents[i];
+        }
+        sage_status e = session.eval({out});
+        if (e) return e;
+        Tensor t;
+        if (!session.get(out, &t)) return C.fail(SAGE_ERR_INVALID, "internal: conv2d result missing");
+        if (C.dry()) return SAGE_OK;
+        return C.check_cuda(cudaMemcpyAsync(static_cast<char *>(y->buf->ptr) + y->offset * 4, t.ptr(), (size_t)out.size() * 4, cudaMemcpyDeviceToDevice,
+                                            C.stream()),
+                            "conv2d result copy");
+    });
+    if (st == SAGE_ERR_INVALID && !g_error.empty() && C.last_error().empty()) C.fail(st, g_error);
+    return st;
+}
+
 // ---------------------------------------------------------------- optimizers
 sage_status sage_sgd_create(float lr, sage_optimizer **out) {
     *out = new sage_optimizer{std::unique_ptr<nn::Optimizer>(new nn::Sgd(lr))};

@@ -48,6 +48,11 @@ struct LayerNorm : Layer {
     void params(std::vector<Var> *p) const override;
 };
 
+struct Softmax : Layer {  // layers.rs:249-273
+    long long axis;
+    explicit Softmax(long long a) : axis(a) {}
+    Var pass(const Var &x) const override { return ops::softmax(x, {axis}); }
+};
 struct Relu : Layer {
     Var pass(const Var &x) const override { return ops::relu(x); }
 };

@@ -455,6 +455,27 @@ def test_conv_pool_vs_oracle(ctx):
     assert rel_err(got, R.avg_pool_2d(RV(x), [19, 17], [19, 17], 0, 1).eval().numpy(), floor=1e-3) <= 1e-4
 
 
+@pytest.mark.parametrize("shape,filt,stride,pad", [((3, 17, 19, 5), (3, 3, 5, 8), 2, 1), ((2, 40, 40, 64), (3, 3, 64, 96), 1, 1)])
+def test_conv2d_entry_point_on_caller_buffers(ctx, shape, filt, stride, pad):
+    """sage_conv2d_nhwc: conv_2d (src/ops/conv.rs:61-96) over buffers the caller owns; the second case has
+    C % 32 == 0 and an image above 128 KiB, so it runs as an implicit GEMM on the tensor cores."""
+    rng = np.random.default_rng(5002)
+    x = rng.standard_normal(shape).astype(np.float32)
+    f = (rng.standard_normal(filt) * 0.1).astype(np.float32)
+    ref = R.conv_2d(RV(x), RV(f), stride, pad, 1).eval().numpy()
+    xt, ft, yt = ctx.tensor(x), ctx.tensor(f), ctx.empty(ref.shape)
+    cx, cf, cy = xt.c(), ft.c(), yt.c()
+    win = S.window(1, stride, pad, 1)
+    import ctypes
+    ctx._ck(S.lib.sage_conv2d_nhwc(ctx.h, ctypes.byref(cx), ctypes.byref(cf), ctypes.byref(win), ctypes.byref(cy)))
+    assert gemm_err(yt.numpy(), ref) <= 1e-4
+    bad = ctx.empty((1, 2, 3, 4)).c()
+    assert S.lib.sage_conv2d_nhwc(ctx.h, ctypes.byref(cx), ctypes.byref(cf), ctypes.byref(win), ctypes.byref(bad)) == 1
+    assert ctx.status_word() == 0
+    for t in (xt, ft, yt):
+        t.release()
+
+
 # ------------------------------------------------------------------------------ models
 def init_params(rng, shapes, std=0.02):
     return [(rng.standard_normal(s) * std).astype(np.float32) for s in shapes]
