@@ -90,6 +90,60 @@ __global__ void __launch_bounds__(256) im2col_kernel(const float *__restrict__ i
     }
 }
 
+// Planes of the column matrix when C is not a multiple of 4 (the first convolution of a network: C = 1 or 3,
+// K = 49 or 147).  A thread owns 4 consecutive entries of a row (one 16-byte store into each plane), so a
+// warp writes 512 contiguous bytes per plane; where an entry comes from (tap, channel) is looked up in a
+// table in shared memory, built once per block, instead of being divided out per element.
+constexpr int kTapTable = 1024;
+__global__ void __launch_bounds__(256) im2col_quads_kernel(const float *__restrict__ img, ColOut o, ConvP p, long long quads) {
+    __shared__ int tab_off[kTapTable];   // element offset of entry kk from the pixel's first tap, -1 beyond K
+    __shared__ int tab_yx[kTapTable];    // (ky * dil_h) << 16 | (kx * dil_w)
+    const int C = (int)p.chan, K = p.w.ker_h * p.w.ker_w * C;
+    for (int kk = threadIdx.x; kk < o.pitch; kk += 256) {
+        if (kk < K) {
+            const int tap = kk / C, c = kk - tap * C;
+            const int ky = tap / p.w.ker_w, kx = tap - ky * p.w.ker_w;
+            tab_off[kk] = (ky * p.w.dil_h * (int)p.img_w + kx * p.w.dil_w) * C + c;
+            tab_yx[kk] = ((ky * p.w.dil_h) << 16) | (kx * p.w.dil_w);
+        } else {
+            tab_off[kk] = -1;
+            tab_yx[kk] = 0;
+        }
+    }
+    __syncthreads();
+    const int per_row = o.pitch >> 2;
+    const unsigned per_img = (unsigned)(p.col_h * p.col_w);
+    for (long long q = (long long)blockIdx.x * 256 + threadIdx.x; q < quads; q += (long long)gridDim.x * 256) {
+        const long long pix = q / per_row;
+        const int k0 = (int)(q - pix * per_row) << 2;
+        const long long n = pix / per_img;
+        const unsigned r = (unsigned)(pix - n * per_img);
+        const int oy = (int)(r / (unsigned)p.col_w), ox = (int)(r % (unsigned)p.col_w);
+        const int iy0 = oy * p.w.stride_h - p.w.pad_h, ix0 = ox * p.w.stride_w - p.w.pad_w;
+        const float *base = img + (n * p.img_h * p.img_w + (long long)iy0 * p.img_w + ix0) * C;
+        float v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int off = tab_off[k0 + i], yx = tab_yx[k0 + i];
+            const int iy = iy0 + (yx >> 16), ix = ix0 + (yx & 0xffff);
+            v[i] = (off >= 0 && ix >= 0 && ix < p.img_w && iy >= 0 && iy < p.img_h) ? __ldg(base + off) : 0.f;
+        }
+        float4 h, l;
+        split_pair(v[0], &h.x, &l.x);
+        split_pair(v[1], &h.y, &l.y);
+        split_pair(v[2], &h.z, &l.z);
+        split_pair(v[3], &h.w, &l.w);
+        float *d = o.hi + pix * o.pitch + k0;
+        *reinterpret_cast<float4 *>(d) = h;
+        *reinterpret_cast<float4 *>(d + o.plane) = l;
+        if (o.col) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (k0 + i < K) o.col[pix * K + k0 + i] = v[i];
+        }
+    }
+}
+
 // Follows the reference's tap test literally, including dilation_h applied to the x tap and
 // dilation_w to the y tap (conv.rs:462-464); identical whenever both dilations are equal.
 __global__ void __launch_bounds__(256) col2im_kernel(const float *__restrict__ col, float *__restrict__ img, ConvP p,
@@ -190,6 +244,12 @@ sage_status im2col_planes(Context &ctx, const float *img, long long n, long long
                 (hi && (reinterpret_cast<uintptr_t>(hi) % 16 || plane % 4 || pitch % 4))))
         return ctx.fail(SAGE_ERR_INVALID, "im2col: unaligned buffer");
     ColOut o{col, hi, plane, pitch};
+    if (!vec && hi && pitch % 4 == 0 && pitch <= kTapTable && reinterpret_cast<uintptr_t>(hi) % 16 == 0 && plane % 4 == 0 &&
+        img_w * (long long)w.ker_h * w.dil_h * chan < (1LL << 30) && w.ker_w * w.dil_w < 65536) {
+        const long long quads = pixels * (pitch / 4);
+        im2col_quads_kernel<<<grid_for(ctx, quads), 256, 0, ctx.stream()>>>(img, o, p, quads);
+        return ctx.check_cuda(cudaGetLastError(), "im2col launch");
+    }
     im2col_kernel<<<(unsigned)((pixels + 7) / 8), 256, 0, ctx.stream()>>>(img, o, p, pixels);
     return ctx.check_cuda(cudaGetLastError(), "im2col launch");
 }
