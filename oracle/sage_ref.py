@@ -1222,3 +1222,72 @@ class Adam:  # optim.rs:97-178
             v_hat = v / (neg(pow_(scalar(self.beta2, [1]), t)) + 1.0)
             p.set((p - m_hat * self.lr / (sqrt(v_hat) + self.eps)).eval())  # :171-173
         self.t = (t + 1.0).eval()  # :176
+
+
+# --------------------------------------------------------------------------- DenseNet, MobileNetV2
+class AvgPool2d:  # layers.rs:90-122
+    def __init__(self, ker, stride=None, pad=0, dil=1):
+        self.a = (ker, ker if stride is None else stride, pad, dil)
+
+    def params(self): return []
+
+    def __call__(self, x): return avg_pool_2d(x, *self.a)
+
+
+class BottleneckLayer:  # models/densenet.rs:121-157
+    def __init__(self, in_planes, out_planes):
+        self.body = Sequential(Relu(), Conv2d(in_planes, out_planes * 4, 1, 1, 0, 1), Conv2d(out_planes * 4, out_planes, 3, 1, 1, 1))
+
+    def params(self): return self.body.params()
+
+    def __call__(self, x): return concat([x, self.body(x)], 3)
+
+
+def densenet(chan_input, num_classes, depth=121, growth_rate=12):  # models/densenet.rs:56-107 (no BatchNorm, no dropout)
+    in_planes = 2 * growth_rate
+    m = Sequential(Conv2d(chan_input, in_planes, 3, 1, 1, 1))
+    n = (depth - 4) // 6
+    for i in range(3):
+        blk = Sequential()
+        for j in range(n):
+            blk.add(BottleneckLayer(in_planes + j * growth_rate, growth_rate))
+        m.add(blk)
+        in_planes += n * growth_rate
+        if i < 2:
+            m.add(Sequential(Relu(), Conv2d(in_planes, in_planes // 2, 1, 1, 0, 1), AvgPool2d(2)))
+            in_planes //= 2
+    m.add(Relu()).add(AdaptiveAvgPool2d([1, 1])).add(Flatten()).add(Dense(in_planes, num_classes))
+    return m
+
+
+def _make_divisible(val, div, min_val):  # models/mobilenet.rs:10-18
+    v = max(min_val, (val + div // 2) // div * div)
+    return v + div if np.float32(v) < np.float32(0.9) * np.float32(val) else v
+
+
+class InvertedResidual:  # models/mobilenet.rs:96-138 (the 3x3 convolution really has padding 0 and dilation 0, :111)
+    def __init__(self, inp, oup, stride, expand_ratio):
+        hidden = inp * expand_ratio
+        self.body = Sequential()
+        if expand_ratio != 1:
+            self.body.add(Conv2d(inp, hidden, 1, 1, 0, 1)).add(Relu())
+        self.body.add(Conv2d(hidden, hidden, 3, stride, 0, 0)).add(Relu()).add(Conv2d(hidden, oup, 1, 1, 0, 1))
+        self.residual = stride == 1 and inp == oup
+
+    def params(self): return self.body.params()
+
+    def __call__(self, x): return x + self.body(x) if self.residual else self.body(x)
+
+
+def mobilenet_v2(chan_in, num_classes):  # models/mobilenet.rs:38-80, width multiplier 1
+    cfg = [(1, 16, 1, 1), (6, 24, 2, 2), (6, 32, 3, 2), (6, 64, 4, 2), (6, 96, 3, 1), (6, 160, 3, 2), (6, 320, 1, 1)]
+    c_in = _make_divisible(32, 8, 8)
+    m = Sequential(Conv2d(chan_in, c_in, 3, 2, 1, 1), Relu())
+    for t, c, n, s in cfg:
+        c_out = _make_divisible(c, 8, 8)
+        for i in range(n):
+            m.add(InvertedResidual(c_in, c_out, s if i == 0 else 1, t))
+            c_in = c_out
+    last = _make_divisible(1280, 8, 8)
+    m.add(Conv2d(c_in, last, 1, 1, 0, 1)).add(Relu()).add(AdaptiveAvgPool2d([1, 1])).add(Flatten()).add(Dense(last, num_classes))
+    return m

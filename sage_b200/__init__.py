@@ -645,6 +645,44 @@ class Bert:
         return _mk(lib.sage_bert_pass, self.h, token_ids.h, attn_mask.h)
 
 
+class _SequentialModel:
+    """A model that is a Sequential in the reference (src/layers.rs:275-325): parameters in traversal order, pass."""
+
+    def __del__(self):
+        try:
+            lib.sage_model_destroy(self.h)
+        except Exception:
+            pass
+
+    def params(self):
+        n = ctypes.c_int32(0)
+        lib.sage_model_params(self.h, None, 0, ctypes.byref(n))
+        out = (_P * n.value)()
+        lib.sage_model_params(self.h, out, n.value, ctypes.byref(n))
+        return [Var(_P(h)) for h in out]
+
+    def pass_(self, x):
+        return _mk(lib.sage_model_pass, self.h, x.h)
+
+
+class DenseNet(_SequentialModel):
+    """DenseNet::new(DenseNetConfig::d121 / d169 / d201) (src/models/densenet.rs:20-107): depth 121 / 169 / 201 with
+    growth rate 12 / 24 / 12."""
+
+    def __init__(self, chan_input, num_classes, depth=121, growth_rate=12):
+        self.h = _P()
+        _gck(lib.sage_densenet_create(ctypes.c_int64(chan_input), ctypes.c_int64(num_classes), ctypes.c_int64(depth),
+                                      ctypes.c_int64(growth_rate), ctypes.byref(self.h)))
+
+
+class MobileNetV2(_SequentialModel):
+    """MobileNetV2::new(MobileNetV2Config::new(chan_in, num_classes)) (src/models/mobilenet.rs:27-80)."""
+
+    def __init__(self, chan_in, num_classes):
+        self.h = _P()
+        _gck(lib.sage_mobilenet_v2_create(ctypes.c_int64(chan_in), ctypes.c_int64(num_classes), ctypes.byref(self.h)))
+
+
 class ResNet18:
     """ResNet::new(ResNetConfig::d18(chan_input, num_classes)) (src/models/resnet.rs:74-104)."""
 

@@ -423,6 +423,18 @@ sage_status sage_resnet18_create(int64_t chan_input, int64_t num_classes, sage_m
         return SAGE_OK;
     });
 }
+sage_status sage_densenet_create(int64_t chan_input, int64_t num_classes, int64_t depth, int64_t growth_rate, sage_model **out) {
+    return guarded([&]() -> sage_status {
+        *out = new sage_model{nn::densenet(chan_input, num_classes, depth, growth_rate)};
+        return SAGE_OK;
+    });
+}
+sage_status sage_mobilenet_v2_create(int64_t chan_in, int64_t num_classes, sage_model **out) {
+    return guarded([&]() -> sage_status {
+        *out = new sage_model{nn::mobilenet_v2(chan_in, num_classes)};
+        return SAGE_OK;
+    });
+}
 sage_status sage_model_destroy(sage_model *m) {
     delete m;
     return SAGE_OK;

@@ -188,5 +188,95 @@ std::shared_ptr<Sequential> resnet18(long long chan_input, long long num_classes
     return m;
 }
 
+// ---------------------------------------------------------------- DenseNet (models/densenet.rs)
+struct BottleneckLayer : Layer {  // densenet.rs:121-157: relu, 1x1 conv to 4 x growth, 3x3 conv to growth; y joins x on the channel axis
+    Sequential body;
+    BottleneckLayer(long long in_planes, long long out_planes) {
+        auto P = [](long long v) { return Pair{v, v}; };
+        body.add(std::make_shared<Relu>());
+        body.add(std::make_shared<Conv2d>(in_planes, out_planes * 4, P(1), P(1), P(0), P(1)));
+        body.add(std::make_shared<Conv2d>(out_planes * 4, out_planes, P(3), P(1), P(1), P(1)));
+    }
+    Var pass(const Var &x) const override { return concat({x, body.pass(x)}, 3); }
+    void params(std::vector<Var> *p) const override { body.params(p); }
+};
+
+std::shared_ptr<Sequential> densenet(long long chan_input, long long num_classes, long long depth, long long growth_rate) {
+    auto P = [](long long v) { return Pair{v, v}; };
+    if (depth < 10 || growth_rate < 1) shape_fail("densenet: depth must be at least 10 and the growth rate positive");
+    long long in_planes = 2 * growth_rate;  // densenet.rs:58-84
+    auto m = std::make_shared<Sequential>();
+    m->add(std::make_shared<Conv2d>(chan_input, in_planes, P(3), P(1), P(1), P(1)));
+    const long long n = (depth - 4) / 6;
+    for (int i = 0; i < 3; ++i) {
+        auto dense = std::make_shared<Sequential>();  // dense_layer, :96-106
+        for (long long j = 0; j < n; ++j) dense->add(std::make_shared<BottleneckLayer>(in_planes + j * growth_rate, growth_rate));
+        m->add(dense);
+        in_planes += n * growth_rate;
+        if (i < 2) {  // transition_layer, :86-94
+            auto t = std::make_shared<Sequential>();
+            t->add(std::make_shared<Relu>());
+            t->add(std::make_shared<Conv2d>(in_planes, in_planes / 2, P(1), P(1), P(0), P(1)));
+            t->add(std::make_shared<AvgPool2d>(P(2), P(2), P(0), P(1)));
+            m->add(t);
+            in_planes /= 2;
+        }
+    }
+    m->add(std::make_shared<Relu>());
+    m->add(std::make_shared<AdaptiveAvgPool2d>(P(1)));
+    m->add(std::make_shared<Flatten>());
+    m->add(std::make_shared<Dense>(in_planes, num_classes));
+    return m;
+}
+
+// ---------------------------------------------------------------- MobileNetV2 (models/mobilenet.rs)
+static long long make_divisible(long long val, long long div, long long min_val) {  // mobilenet.rs:10-18
+    const long long v = std::max(min_val, (val + div / 2) / div * div);
+    return (float)v < 0.9f * (float)val ? v + div : v;
+}
+
+struct InvertedResidual : Layer {  // mobilenet.rs:96-138
+    Sequential body;
+    bool residual;
+    InvertedResidual(long long inp, long long oup, long long stride, long long expand_ratio) : residual(stride == 1 && inp == oup) {
+        auto P = [](long long v) { return Pair{v, v}; };
+        const long long hidden = inp * expand_ratio;
+        if (expand_ratio != 1) {
+            body.add(std::make_shared<Conv2d>(inp, hidden, P(1), P(1), P(0), P(1)));
+            body.add(std::make_shared<Relu>());
+        }
+        // the reference passes padding 0 and dilation 0 here (mobilenet.rs:111): a full 3 x 3 convolution whose
+        // nine taps all read the pixel at the window's corner
+        body.add(std::make_shared<Conv2d>(hidden, hidden, P(3), P(stride), P(0), P(0)));
+        body.add(std::make_shared<Relu>());
+        body.add(std::make_shared<Conv2d>(hidden, oup, P(1), P(1), P(0), P(1)));
+    }
+    Var pass(const Var &x) const override { return residual ? add(x, body.pass(x)) : body.pass(x); }
+    void params(std::vector<Var> *p) const override { body.params(p); }
+};
+
+std::shared_ptr<Sequential> mobilenet_v2(long long chan_in, long long num_classes) {  // mobilenet.rs:38-80, width_mul 1
+    auto P = [](long long v) { return Pair{v, v}; };
+    static const long long cfg[7][4] = {{1, 16, 1, 1}, {6, 24, 2, 2}, {6, 32, 3, 2}, {6, 64, 4, 2}, {6, 96, 3, 1}, {6, 160, 3, 2}, {6, 320, 1, 1}};
+    long long c_in = make_divisible(32, 8, 8);
+    auto m = std::make_shared<Sequential>();
+    m->add(std::make_shared<Conv2d>(chan_in, c_in, P(3), P(2), P(1), P(1)));
+    m->add(std::make_shared<Relu>());
+    for (auto &row : cfg) {
+        const long long c_out = make_divisible(row[1], 8, 8);
+        for (long long i = 0; i < row[2]; ++i) {
+            m->add(std::make_shared<InvertedResidual>(c_in, c_out, i == 0 ? row[3] : 1, row[0]));
+            c_in = c_out;
+        }
+    }
+    const long long last = make_divisible(1280, 8, 8);
+    m->add(std::make_shared<Conv2d>(c_in, last, P(1), P(1), P(0), P(1)));  // Conv2d::new(in, out, 1): stride 1, padding 0, dilation 1
+    m->add(std::make_shared<Relu>());
+    m->add(std::make_shared<AdaptiveAvgPool2d>(P(1)));
+    m->add(std::make_shared<Flatten>());
+    m->add(std::make_shared<Dense>(last, num_classes));
+    return m;
+}
+
 }  // namespace nn
 }  // namespace sage

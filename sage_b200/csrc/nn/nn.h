@@ -64,6 +64,11 @@ struct MaxPool2d : Layer {
     MaxPool2d(ops::Pair k, ops::Pair s, ops::Pair p, ops::Pair d) : ker(k), stride(s), pad(p), dil(d) {}
     Var pass(const Var &x) const override { return ops::max_pool_2d(x, ker, stride, pad, dil); }
 };
+struct AvgPool2d : Layer {  // layers.rs:90-122
+    ops::Pair ker, stride, pad, dil;
+    AvgPool2d(ops::Pair k, ops::Pair s, ops::Pair p, ops::Pair d) : ker(k), stride(s), pad(p), dil(d) {}
+    Var pass(const Var &x) const override { return ops::avg_pool_2d(x, ker, stride, pad, dil); }
+};
 struct AdaptiveAvgPool2d : Layer {
     ops::Pair ext;
     explicit AdaptiveAvgPool2d(ops::Pair e) : ext(e) {}
@@ -121,6 +126,11 @@ struct Bert {
 
 // models/resnet.rs:74-129 with ResNetConfig::d18 (BatchNorm is commented out in the reference).
 std::shared_ptr<Sequential> resnet18(long long chan_input, long long num_classes);
+// models/densenet.rs:56-107: DenseNetConfig::d121 / d169 / d201 are (depth, growth rate) = (121, 12), (169, 24), (201, 12);
+// BatchNorm and dropout are declared in the reference's config but never applied.
+std::shared_ptr<Sequential> densenet(long long chan_input, long long num_classes, long long depth, long long growth_rate);
+// models/mobilenet.rs:38-80 with MobileNetV2Config::new (width multiplier 1).
+std::shared_ptr<Sequential> mobilenet_v2(long long chan_in, long long num_classes);
 
 }  // namespace nn
 }  // namespace sage

@@ -554,6 +554,34 @@ def test_resnet18_vs_oracle(ctx):
 
 
 # ------------------------------------------------------------------------------ runtime behaviour
+@pytest.mark.parametrize("name,shape", [("densenet121", (8, 32, 32, 3)), ("densenet169", (2, 16, 16, 1)), ("mobilenet_v2", (4, 64, 64, 3))])
+def test_densenet_and_mobilenet_vs_oracle(ctx, name, shape):
+    """The reference's other two image models (src/models/densenet.rs, src/models/mobilenet.rs) as it builds them:
+    DenseNet without BatchNorm or dropout, channel concatenation after every bottleneck; MobileNetV2 with full
+    3 x 3 convolutions of padding 0 and dilation 0.  Logits rel <= 1e-3 against the oracle evaluating the same graph."""
+    rng = np.random.default_rng(5100)
+    if name == "densenet121":
+        model, rmodel = S.DenseNet(shape[3], 10), R.densenet(shape[3], 10)
+    elif name == "densenet169":
+        model, rmodel = S.DenseNet(shape[3], 7, 169, 24), R.densenet(shape[3], 7, 169, 24)
+    else:
+        model, rmodel = S.MobileNetV2(shape[3], 10), R.mobilenet_v2(shape[3], 10)
+    params, rparams = model.params(), rmodel.params()
+    assert [tuple(p.extents) for p in params] == [tuple(r.extents) for r in rparams]
+    for p, r in zip(params, rparams):
+        e = p.extents
+        v = (rng.standard_normal(e) * (np.sqrt(1.0 / (e[0] * e[1] * e[2])) if len(e) == 4 else 0.05)).astype(np.float32)
+        ctx.set(p, v)
+        r.set(v.copy())
+    x = rng.standard_normal(shape).astype(np.float32)
+    got = model.pass_(ctx.var(x)).eval(ctx)
+    ref = rmodel(RV(x)).eval().numpy()
+    assert got.shape == ref.shape and np.isfinite(ref).all() and float(np.abs(ref).max()) > 0
+    assert gemm_err(got, ref) <= 1e-3
+    assert ctx.status_word() == 0
+    ctx.clear()
+
+
 def test_bounded_wait_runs_out_and_reports():
     """Every device-side wait has a limit.  The self-test kernel waits on a barrier nothing arrives on:
     after about a second the wait gives up, the kernel returns, the status word says so, and the
