@@ -116,6 +116,11 @@ sage_status sage_op_softmax_cross_entropy(const sage_var *x, const sage_var *lab
 sage_status sage_op_layer_norm(const sage_var *x, int32_t naxes, const int64_t *axes, const sage_var *gamma,
                                const sage_var *beta, float eps, sage_var **out);                                  /* :84-100 */
 
+/* ---- random tensors, src/ops/rand.rs:21-140.  The reference takes two 32-bit seeds from the thread's generator at
+ * every evaluation; here the caller gives them, so results can be reproduced.  uniform: [0, 1]; normal: Box-Muller. */
+sage_status sage_op_uniform(int32_t ndim, const int64_t *extents, uint32_t seed_x, uint32_t seed_y, sage_var **out);
+sage_status sage_op_normal(int32_t ndim, const int64_t *extents, uint32_t seed_x, uint32_t seed_y, sage_var **out);
+
 /* ---- metric, src/ops/metric.rs:4-17: share of rows whose argmax(logits, 1) equals the label */
 sage_status sage_op_accuracy(const sage_var *logits, const sage_var *labels, sage_var **out);
 

@@ -1291,3 +1291,43 @@ def mobilenet_v2(chan_in, num_classes):  # models/mobilenet.rs:38-80, width mult
     last = _make_divisible(1280, 8, 8)
     m.add(Conv2d(c_in, last, 1, 1, 0, 1)).add(Relu()).add(AdaptiveAvgPool2d([1, 1])).add(Flatten()).add(Dense(last, num_classes))
     return m
+
+
+# --------------------------------------------------------------------------- random tensors (ops/rand.rs)
+def _xorshift128(seed_x, seed_y):  # rand.rs:40-48 on uint32 arrays; the literal is a double in OpenCL C
+    t = seed_x ^ (seed_x << np.uint32(11))
+    r = seed_y ^ (seed_y >> np.uint32(19)) ^ (t ^ (t >> np.uint32(8)))
+    return (r.astype(np.float64) * 2.3283064e-10).astype(np.float32)
+
+
+class _Rand:
+    def __init__(self, normal, seed_x, seed_y, extents):
+        self.normal, self.sx, self.sy, self.extents = normal, np.uint32(seed_x), np.uint32(seed_y), extents
+
+    def compute(self, _):
+        n = int(np.prod(self.extents))
+        with np.errstate(over="ignore", divide="ignore", invalid="ignore"):
+            if not self.normal:  # rand.rs:69-72
+                g = np.arange(n, dtype=np.uint32)
+                y = _xorshift128(self.sx + g, self.sy + g)
+            else:  # rand.rs:108-121; the store past the end of an odd-sized tensor is dropped
+                g = np.arange((n + 1) // 2, dtype=np.uint32)
+                u1 = _xorshift128(self.sx + g * np.uint32(2), np.full_like(g, self.sy))
+                u2 = _xorshift128(self.sx + g * np.uint32(2) + np.uint32(1), np.full_like(g, self.sy))
+                r = np.sqrt(np.float32(-2.0) * np.log(u1))
+                theta = (2.0 * math.pi * u2.astype(np.float64)).astype(np.float32)
+                y = np.stack([r * np.cos(theta), r * np.sin(theta)], axis=1).reshape(-1)[:n].astype(np.float32)
+        return Tensor(np.ascontiguousarray(y, dtype=np.float32), Shape(self.extents), FLOAT)
+
+    def grad(self, x, y, gy):
+        return []
+
+
+def uniform(extents, seed_x, seed_y):  # rand.rs:21-28; the reference draws the seeds itself
+    e = to_extents(extents, 0)
+    return Var(Shape(e), FLOAT, _Rand(False, seed_x, seed_y, e), [])
+
+
+def normal(extents, seed_x, seed_y):  # rand.rs:30-38
+    e = to_extents(extents, 0)
+    return Var(Shape(e), FLOAT, _Rand(True, seed_x, seed_y, e), [])

@@ -565,6 +565,16 @@ def grad_param(y, model):
     return dict(zip(params, grad(y, params)))
 
 
+def uniform(extents, seed_x, seed_y):
+    """ops::rand::uniform (src/ops/rand.rs:21-28, 50-90) with explicit seeds: values in [0, 1]."""
+    return _mk(lib.sage_op_uniform, len(extents), _arr64(extents), ctypes.c_uint32(seed_x), ctypes.c_uint32(seed_y))
+
+
+def normal(extents, seed_x, seed_y):
+    """ops::rand::normal (src/ops/rand.rs:30-38, 92-140) with explicit seeds: Box-Muller pairs."""
+    return _mk(lib.sage_op_normal, len(extents), _arr64(extents), ctypes.c_uint32(seed_x), ctypes.c_uint32(seed_y))
+
+
 def accuracy(logits, labels):
     """ops::metric::accuracy (src/ops/metric.rs:4-17)."""
     return _mk(lib.sage_op_accuracy, logits.h, labels.h)

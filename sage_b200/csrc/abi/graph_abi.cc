@@ -291,6 +291,12 @@ sage_status sage_op_layer_norm(const sage_var *x, int32_t naxes, const int64_t *
     OP(ops::layer_norm(x->v, axes_of(naxes, axes), gamma->v, beta->v, eps));
 }
 
+sage_status sage_op_uniform(int32_t ndim, const int64_t *extents, uint32_t seed_x, uint32_t seed_y, sage_var **out) {
+    OP(ops::uniform(arr(ndim, extents), seed_x, seed_y));
+}
+sage_status sage_op_normal(int32_t ndim, const int64_t *extents, uint32_t seed_x, uint32_t seed_y, sage_var **out) {
+    OP(ops::normal(arr(ndim, extents), seed_x, seed_y));
+}
 sage_status sage_op_accuracy(const sage_var *logits, const sage_var *labels, sage_var **out) { OP(ops::accuracy(logits->v, labels->v)); }
 
 // conv_2d over caller-owned buffers (declared in sage_cuda.h; lives here because the lowering to an implicit

@@ -250,6 +250,9 @@ Var softmax_cross_entropy(const Var &x, const Var &labels);
 Var layer_norm(const Var &x, const std::vector<long long> &axes, const Var &gamma, const Var &beta, float eps);
 // metric.rs
 Var accuracy(const Var &logits, const Var &labels);
+// rand.rs (the seeds the reference draws per evaluation are arguments here)
+Var uniform(const Array &extents, unsigned seed_x, unsigned seed_y);
+Var normal(const Array &extents, unsigned seed_x, unsigned seed_y);
 // arithmetic sugar (map.rs:1180-1370)
 inline Var add(const Var &a, const Var &b) { return binary_map(a, b, Add); }
 inline Var sub(const Var &a, const Var &b) { return binary_map(a, b, Sub); }

@@ -290,4 +290,30 @@ Var ops::concat(const std::vector<Var> &xs, long long axis) {
     return Var::from_op(op, xs);
 }
 
+// ---------------------------------------------------------------- uniform / normal (src/ops/rand.rs:21-140)
+// The reference draws the two seeds from the thread's generator at every evaluation; here they belong to
+// the operator, so an evaluation can be repeated.
+struct RandOp : Operator {
+    bool normal;
+    unsigned seed_x, seed_y;
+    const char *name() const override { return normal ? "normal" : "uniform"; }
+    std::vector<Var> grad(const std::vector<Var> &, const Var &, const Var &) override { return {}; }
+    sage_status compute(const std::vector<Tensor> &, Context &ctx, Tensor *y) override {
+        sage_status st = Tensor::uninit(ctx, out, y);
+        if (st) return st;
+        return k::rand_fill(ctx, normal, (float *)y->ptr(), out.shape.size(), seed_x, seed_y);
+    }
+};
+
+static Var make_rand(bool normal, const Array &extents, unsigned seed_x, unsigned seed_y) {
+    auto op = std::make_shared<RandOp>();
+    op->normal = normal;
+    op->seed_x = seed_x;
+    op->seed_y = seed_y;
+    op->out = TensorDesc(infer_extents(extents, 0), SAGE_F32);
+    return Var::from_op(op, {});
+}
+Var ops::uniform(const Array &extents, unsigned seed_x, unsigned seed_y) { return make_rand(false, extents, seed_x, seed_y); }
+Var ops::normal(const Array &extents, unsigned seed_x, unsigned seed_y) { return make_rand(true, extents, seed_x, seed_y); }
+
 }  // namespace sage

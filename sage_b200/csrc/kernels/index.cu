@@ -129,5 +129,47 @@ sage_status strided_copy(Context &ctx, const uint32_t *x, const Dims &dims, uint
     return ctx.check_cuda(cudaGetLastError(), "strided_copy launch");
 }
 
+// ---------------------------------------------------------------- random fills (src/ops/rand.rs:40-140)
+// The reference's generator: one xorshift-style mix of two 32-bit seeds per element (rand.rs:40-48), the
+// product with 2.3283064e-10 taken in double precision as OpenCL C does for an unsuffixed literal.
+__device__ __forceinline__ float xorshift128(unsigned seed_x, unsigned seed_y) {
+    const unsigned t = seed_x ^ (seed_x << 11);
+    const unsigned rndint = seed_y ^ (seed_y >> 19) ^ (t ^ (t >> 8));
+    return (float)((double)rndint * 2.3283064e-10);
+}
+
+__global__ void __launch_bounds__(256) rand_uniform_kernel(float *__restrict__ y, unsigned seed_x, unsigned seed_y, long long n) {
+    grid_dependency_sync();
+    for (long long g = (long long)blockIdx.x * 256 + threadIdx.x; g < n; g += (long long)gridDim.x * 256)
+        y[g] = xorshift128(seed_x + (unsigned)g, seed_y + (unsigned)g);  // rand.rs:69-72
+}
+
+// Box-Muller on pairs (rand.rs:108-121); theta is formed in double like `2 * M_PI * u2` in OpenCL C.  The
+// reference writes y[2 gid + 1] even when the tensor has an odd number of elements; here that store is skipped.
+__global__ void __launch_bounds__(256) rand_normal_kernel(float *__restrict__ y, unsigned seed_x, unsigned seed_y, long long n) {
+    grid_dependency_sync();
+    const long long pairs = (n + 1) / 2;
+    for (long long g = (long long)blockIdx.x * 256 + threadIdx.x; g < pairs; g += (long long)gridDim.x * 256) {
+        const float u1 = xorshift128(seed_x + (unsigned)g * 2u, seed_y);
+        const float u2 = xorshift128(seed_x + (unsigned)g * 2u + 1u, seed_y);
+        const float rsq = -2.f * logf(u1);
+        const float theta = (float)(2.0 * 3.14159265358979323846 * (double)u2);
+        const float r = sqrtf(rsq);
+        y[2 * g] = r * cosf(theta);
+        if (2 * g + 1 < n) y[2 * g + 1] = r * sinf(theta);
+    }
+}
+
+sage_status rand_fill(Context &ctx, bool normal, float *y, long long n, unsigned seed_x, unsigned seed_y) {
+    ctx.note_launch(normal ? "rand_normal" : "rand_uniform");
+    if (ctx.dry() || n == 0) return SAGE_OK;
+    const long long work = normal ? (n + 1) / 2 : n;
+    if (normal)
+        launch_dependent(ctx.pdl, ctx.stream(), rand_normal_kernel, dim3(grid_for(ctx, work)), dim3(256), 0, y, seed_x, seed_y, n);
+    else
+        launch_dependent(ctx.pdl, ctx.stream(), rand_uniform_kernel, dim3(grid_for(ctx, work)), dim3(256), 0, y, seed_x, seed_y, n);
+    return ctx.check_cuda(cudaGetLastError(), "rand launch");
+}
+
 }  // namespace k
 }  // namespace sage

@@ -42,6 +42,9 @@ sage_status scatter_add(Context &ctx, const float *x, const long long *x_str, co
 // y[translate(g, dims.ext, y_str)] = x[translate(g, dims.ext, dims.str)]
 sage_status strided_copy(Context &ctx, const uint32_t *x, const Dims &dims, uint32_t *y, const long long *y_str);
 
+// Uniform::compute / Normal::compute (src/ops/rand.rs:50-140) with the two 32-bit seeds given by the caller.
+sage_status rand_fill(Context &ctx, bool normal, float *y, long long n, unsigned seed_x, unsigned seed_y);
+
 // conv.cu — im2col / col2im / direct pooling (src/ops/conv.rs:143-165, 289-498)
 struct Window {
     int ker_w, ker_h, stride_w, stride_h, pad_w, pad_h, dil_w, dil_h;

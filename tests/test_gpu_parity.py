@@ -582,6 +582,25 @@ def test_densenet_and_mobilenet_vs_oracle(ctx, name, shape):
     ctx.clear()
 
 
+def test_random_tensors_with_explicit_seeds(ctx):
+    """ops::rand::uniform / normal (src/ops/rand.rs): the reference's one-round xorshift mix of (seed + index), with
+    the seeds as arguments.  uniform is integer arithmetic and one correctly rounded product: equal bits;
+    normal goes through log / sqrt / cos / sin: |a - b| <= 1e-5 (values of order 1)."""
+    for extents, sx, sy in (([3, 1001], 12345, 678), ([4096], 0xFFFFFFF0, 0xDEADBEEF), ([1], 1, 2), ([5, 7, 3], 42, 43)):
+        got = S.uniform(extents, sx, sy).eval(ctx)
+        ref = R.uniform(extents, sx, sy).eval().numpy()
+        assert got.shape == ref.shape and np.array_equal(got, ref)
+        assert (got >= 0).all() and (got <= 1).all()
+        gz = S.normal(extents, sx, sy).eval(ctx)
+        rz = R.normal(extents, sx, sy).eval().numpy()
+        ok = np.isfinite(rz)
+        assert gz.shape == rz.shape and np.array_equal(np.isfinite(gz), ok)
+        assert np.abs(gz[ok] - rz[ok]).max(initial=0.0) <= 1e-5 * max(1.0, float(np.abs(rz[ok]).max(initial=0.0)))
+    a, b = S.uniform([64], 5, 6), S.uniform([64], 5, 6)
+    assert np.array_equal(a.eval(ctx), b.eval(ctx))      # same seeds, same tensor
+    ctx.clear()
+
+
 def test_bounded_wait_runs_out_and_reports():
     """Every device-side wait has a limit.  The self-test kernel waits on a barrier nothing arrives on:
     after about a second the wait gives up, the kernel returns, the status word says so, and the
