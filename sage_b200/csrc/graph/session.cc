@@ -391,11 +391,6 @@ static std::vector<RowGroupPlan> plan_row_groups(const std::vector<Var> &order, 
             exchanges[i] = row_program_exchanges(*probe) > 0;
             row_program_space(*probe, &R[i], &C[i]);
         }
-        if (getenv("SAGE_ROW_GROUP_DEBUG")) {
-            std::string e;
-            for (long long x : order[i].extents()) e += std::to_string(x) + ",";
-            fprintf(stderr, "state %d %s [%s] ok=%d space=%lldx%lld reads=%zu\n", i, order[i].origin->op->name(), e.c_str(), (int)ok[i], R[i], C[i], in.size());
-        }
     }
     std::vector<int> group(n);
     std::vector<std::vector<int>> members(n);

@@ -382,3 +382,34 @@ def test_out_of_memory_evicts_recomputes_and_gives_the_same_values():
             c.close()
     assert np.array_equal(outs[0], outs[1]) and np.isfinite(outs[0]).all()
     assert launches[1] > launches[0]   # states were evicted and computed again
+
+
+def test_row_groups_do_not_swallow_a_state_that_lies_between_them():
+    """a (row space) feeds a GEMM g and, together with g, a second row-space state b.  Merging a and b into
+    one kernel would need g both after and before it; they stay two generated kernels around the GEMM, and
+    the values match the kernel-by-kernel evaluation and float64."""
+    rng = np.random.default_rng(950)
+    x = rng.standard_normal((192, 256)).astype(np.float32)
+    w = (rng.standard_normal((256, 256)) / 16).astype(np.float32)
+    outs = []
+    for fusion in (1, 5):
+        c = S.Context(0, pattern_fusion=fusion)
+        try:
+            xv, wv = c.var(x), c.var(w)
+            a = (xv - xv.max([1], True)).exp()
+            g = S.matmul(a, wv)
+            b = ((a + g) * a).sum([1], False) + a.sum([1], False)
+            c.trace_begin()
+            c.eval(b, g)
+            t = c.trace()
+            if fusion == 1:
+                assert t.count("sage_row_program") == 2 and t.index("sage_row_program") < t.index("gemm_tc_3xtf32") < len(t) - 1 - t[::-1].index("sage_row_program")
+            outs.append((c.read(b), c.read(g)))
+        finally:
+            c.close()
+    for p, q in zip(*outs):
+        assert gemm_err(p, q) <= 1e-4
+    A = np.exp(np.maximum(x.astype(np.float64) - np.maximum(x.max(1, keepdims=True), 0), -1e30))  # the reference's max starts from 0
+    G = A @ w.astype(np.float64)
+    B = ((A + G) * A).sum(1) + A.sum(1)
+    assert gemm_err(outs[0][0], B.astype(np.float32)) <= 1e-4 and gemm_err(outs[0][1], G.astype(np.float32)) <= 1e-4
