@@ -369,7 +369,7 @@ struct RowGroupPlan {
 static std::vector<RowGroupPlan> plan_row_groups(const std::vector<Var> &order, const std::unordered_map<Origin *, std::vector<Var>> &inputs) {
     const int n = (int)order.size();
     std::vector<RowGroupPlan> plans;
-    if (n < 2 || n > 8192) return plans;
+    if (n < 1 || n > 4096) return plans;  // the legality test is quadratic in the number of states
     std::unordered_map<Origin *, int> index;
     for (int i = 0; i < n; ++i) index[order[i].key()] = i;
     const int words = (n + 63) / 64;
