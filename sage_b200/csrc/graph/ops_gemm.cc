@@ -358,8 +358,44 @@ struct GemmOp : Operator {
             g.aux[i].sr = gs[GRow];
             g.aux[i].sc = (int)gs[GCol];
         }
+        // An epilogue cannot be applied before the K slices of a split product are summed.  Where the cost model
+        // wants slices (few output tiles, long K: a convolution of a small feature map at a small batch), the
+        // plain product goes to scratch and the epilogue runs as a generated map kernel over the sum.
+        if (!g.epilogue.empty() && !g.row_softmax && !g.conv.on && !folded && batch == 1 && g.c && epi_ext == out.shape.extents) {
+            k::TcGemm raw = g;
+            raw.epilogue.clear();
+            raw.naux = 0;
+            raw.c_hi = nullptr;
+            raw.ldc = n;
+            raw.sc0 = m * n;
+            raw.sc1 = 0;
+            raw.nbc0 = 1;
+            if (k::gemm_tc_split_plan(ctx, raw) >= 2) {
+                Block *sum = ctx.allocator().alloc((size_t)(m * n) * sizeof(float));
+                if (sum) {
+                    raw.c = reinterpret_cast<float *>(sum->ptr);
+                    st = k::gemm_tc_run(ctx, raw);
+                    if (!st) {
+                        std::vector<MapOperand> operands(1 + (size_t)g.naux);
+                        operands[0].dtype = SAGE_F32;
+                        operands[0].ptr = raw.c;
+                        operands[0].view = Tensor().with_shape(Shape(out.shape.extents)).dims();
+                        for (int i = 0; i < g.naux; ++i) {
+                            operands[1 + i].dtype = x[2 + i].desc.dtype;
+                            operands[1 + i].ptr = x[2 + i].ptr();
+                            operands[1 + i].view = x[2 + i].dims();
+                        }
+                        st = map_launch(ctx, epilogue, operands, SAGE_F32, y->ptr(), out.shape.rank(), out.shape.extents.data(), &epi_cache, g.c_hi,
+                                        g.c_plane);
+                    }
+                    ctx.allocator().free(sum);  // stream-ordered
+                    return st;
+                }
+            }
+        }
         return k::gemm_tc_run(ctx, g);
     }
+    MapCache epi_cache;  // the epilogue as a map kernel, for products that are cut into K slices
 
     // Each group's axes must step through the operand like one axis (or not at all), and the
     // column group with stride 0 or 1.

@@ -136,6 +136,9 @@ struct TcGemm {
 };
 bool gemm_tc_shape_ok(long long m, long long n, long long k, long long batch);
 sage_status gemm_tc_run(Context &ctx, const TcGemm &g);
+// How many K slices gemm_tc_run would cut this product into (0 = none).  Only products without an epilogue are
+// cut; a caller with an epilogue may ask for the plain product and apply the epilogue to the sum itself.
+int gemm_tc_split_plan(Context &ctx, const TcGemm &g);
 // hi/lo split of `n` consecutive floats into planes laid out like the source (dst_hi[i], dst_hi[plane + i]).
 sage_status split_tf32_flat(Context &ctx, const float *src, long long n, float *dst_hi, long long plane);
 // hi/lo split of a strided 4-level view (b1, b0, row, col) into compact planes owned by `out`.

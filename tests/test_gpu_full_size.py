@@ -1,9 +1,10 @@
 """BASELINE configs 4 and 5 at their full sizes.  The CPU oracle cannot evaluate them in reasonable
 time, so the full batch is checked through properties that do not depend on size:
 
-  * a forward pass is independent per sample, and every output element is accumulated in the same
-    order whatever the batch, so the first rows of the full-batch result must equal — bit for bit —
-    the result of evaluating those samples alone;
+  * a forward pass is independent per sample: the first rows of the full-batch result must equal the
+    result of evaluating those samples alone — bit for bit where the batch size does not change how a
+    product is tiled (ResNet, 64 of 256 images), to fp32 rounding where it does (small batches cut long-K
+    products into K slices);
   * shuffling the batch shuffles the outputs (again bit for bit);
   * the small batch itself is compared with the oracle (rel <= 1e-3 on logits).
 
@@ -61,7 +62,10 @@ def test_config4_bert_large_full_batch():
               (batch, dt, batch / dt, ctx.mem_stats()["mem_peak"] / 1e9))
         assert full.shape == (batch, 2) and np.isfinite(full).all() and np.array_equal(full, full2)
         small, _ = run(np.arange(2))
-        assert np.array_equal(full[:2], small)                      # per-sample independence, bit for bit
+        # per-sample independence.  Not bit for bit: at 2 sequences the projections have so few output tiles that
+        # they are cut into K slices (another summation order than at 256 sequences); a contraction's error is
+        # measured against the rms of its outputs
+        assert float(np.abs(small - full[:2]).max() / np.sqrt((full[:2].astype(np.float64) ** 2).mean())) <= 1e-5
         perm = rng.permutation(batch)
         shuffled, _ = run(perm)
         assert np.array_equal(shuffled, full[perm])                 # batch order does not matter
