@@ -214,54 +214,75 @@ static RDims canonical_inner(const Dims &in) {
 }
 
 // Column reduction: x is [rows, cols] with unit column stride and `pitch` elements between rows; y[c]
-// combines x[r, c] over the rows of this block's chunk (blockIdx.y).  A warp reads 32 consecutive
-// columns of a row (one 128-byte line); the 8 warps of a block take rows 8 apart, four rows in flight
-// each.  With more than one chunk the partial results go to scratch [chunks, cols] and a second launch
+// combines x[r, c] over the rows of this block's chunk (blockIdx.y).  A warp reads 32 * VEC consecutive
+// columns of a row (128 or, with 16-byte loads, 512 contiguous bytes); the 8 warps of a block take rows 8
+// apart, four rows in flight each.  With more than one chunk the partial results go to scratch [chunks, cols] and a second launch
 // of the same kernel combines them: the order of combination is fixed, so results repeat bit for bit.
-template <typename T>
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256) reduce_cols_kernel(const T *__restrict__ x, T *__restrict__ y, long long rows, long long cols,
                                                           long long pitch, long long rows_per_chunk, int kind, int ref_compat) {
     grid_dependency_sync();
-    __shared__ T part[8][33];
+    struct alignas(sizeof(T) * VEC) Vec {
+        T v[VEC];
+    };
+    __shared__ T part[8][32 * VEC + 1];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const long long col = (long long)blockIdx.x * 32 + tx;
+    const long long col = ((long long)blockIdx.x * 32 + tx) * VEC;  // VEC consecutive columns per lane (cols % VEC == 0)
     const long long r0 = (long long)blockIdx.y * rows_per_chunk;
     const long long r1 = r0 + rows_per_chunk < rows ? r0 + rows_per_chunk : rows;
-    T acc = Ops<T>::identity(kind), a1 = acc, a2 = acc, a3 = acc;
+    T acc[4][VEC];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[u][e] = Ops<T>::identity(kind);
     if (col < cols) {
         const T *base = x + col;
         long long r = r0 + ty;
-        for (; r + 24 < r1; r += 32) {
-            const T v0 = base[r * pitch], v1 = base[(r + 8) * pitch], v2 = base[(r + 16) * pitch], v3 = base[(r + 24) * pitch];
-            acc = Ops<T>::apply(kind, acc, v0);
-            a1 = Ops<T>::apply(kind, a1, v1);
-            a2 = Ops<T>::apply(kind, a2, v2);
-            a3 = Ops<T>::apply(kind, a3, v3);
-        }
-        for (; r < r1; r += 8) acc = Ops<T>::apply(kind, acc, base[r * pitch]);
-        acc = Ops<T>::apply(kind, Ops<T>::apply(kind, acc, a1), Ops<T>::apply(kind, a2, a3));
-    }
-    part[ty][tx] = acc;
-    __syncthreads();
-    if (ty == 0 && col < cols) {
+        for (; r + 24 < r1; r += 32) {  // four rows in flight per thread
+            Vec v[4];
 #pragma unroll
-        for (int i = 1; i < 8; ++i) acc = Ops<T>::apply(kind, acc, part[i][tx]);
-        if (ref_compat) acc = Ops<T>::apply(kind, (T)0, acc);
-        y[(long long)blockIdx.y * cols + col] = acc;
+            for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const Vec *>(base + (r + 8 * u) * pitch);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) acc[u][e] = Ops<T>::apply(kind, acc[u][e], v[u].v[e]);
+        }
+        for (; r < r1; r += 8) {
+            const Vec v = *reinterpret_cast<const Vec *>(base + r * pitch);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) acc[0][e] = Ops<T>::apply(kind, acc[0][e], v.v[e]);
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+        part[ty][tx * VEC + e] = Ops<T>::apply(kind, Ops<T>::apply(kind, acc[0][e], acc[1][e]), Ops<T>::apply(kind, acc[2][e], acc[3][e]));
+    __syncthreads();
+    // the 8 partial rows are combined in a fixed order; 32 * VEC columns spread over the 256 threads
+    for (int c = threadIdx.x; c < 32 * VEC; c += 256) {
+        const long long out_col = (long long)blockIdx.x * 32 * VEC + c;
+        if (out_col >= cols) continue;
+        T a = part[0][c];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) a = Ops<T>::apply(kind, a, part[i][c]);
+        if (ref_compat) a = Ops<T>::apply(kind, (T)0, a);
+        y[(long long)blockIdx.y * cols + out_col] = a;
     }
 }
 
 template <typename T>
 static sage_status launch_reduce_cols(Context &ctx, int kind, const T *x, long long rows, long long cols, long long pitch, T *y, int compat_in) {
     const int compat = compat_in < 0 ? ctx.opts().ref_compat : compat_in;
-    const long long tiles = (cols + 31) / 32;
+    // 16-byte loads (4 columns per lane) when the rows allow; the second stage reads scratch with pitch = cols
+    const bool vec = cols % 4 == 0 && pitch % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && cols >= 256;
+    const long long tiles = vec ? (cols + 127) / 128 : (cols + 31) / 32;
+    auto kernel = vec ? reduce_cols_kernel<T, 4> : reduce_cols_kernel<T, 1>;
     long long chunks = (2LL * ctx.sm_count + tiles - 1) / tiles;
     chunks = std::max(1LL, std::min(chunks, rows / 64));
     ctx.note_launch("reduce_cols");
     if (chunks > 1) ctx.note_launch("reduce_cols");
     if (ctx.dry()) return SAGE_OK;
     if (chunks == 1) {
-        launch_dependent(ctx.pdl, ctx.stream(), reduce_cols_kernel<T>, dim3((unsigned)tiles, 1), dim3(256), 0, x, y, rows, cols, pitch, rows, kind, compat);
+        launch_dependent(ctx.pdl, ctx.stream(), kernel, dim3((unsigned)tiles, 1), dim3(256), 0, x, y, rows, cols, pitch, rows, kind, compat);
         return ctx.check_cuda(cudaGetLastError(), "reduce_cols launch");
     }
     const long long per = (rows + chunks - 1) / chunks;
@@ -270,9 +291,9 @@ static sage_status launch_reduce_cols(Context &ctx, int kind, const T *x, long l
     if (!scratch) return ctx.fail(SAGE_ERR_OOM, "out of memory for the partial results of a column reduction");
     T *partial = reinterpret_cast<T *>(scratch->ptr);
     // the accumulator rule (start from 0) is applied once, by the second stage
-    launch_dependent(ctx.pdl, ctx.stream(), reduce_cols_kernel<T>, dim3((unsigned)tiles, (unsigned)chunks), dim3(256), 0, x, partial, rows, cols, pitch, per,
+    launch_dependent(ctx.pdl, ctx.stream(), kernel, dim3((unsigned)tiles, (unsigned)chunks), dim3(256), 0, x, partial, rows, cols, pitch, per,
                      kind, 0);
-    launch_dependent(ctx.pdl, ctx.stream(), reduce_cols_kernel<T>, dim3((unsigned)tiles, 1), dim3(256), 0, (const T *)partial, y, chunks, cols, cols, chunks,
+    launch_dependent(ctx.pdl, ctx.stream(), kernel, dim3((unsigned)tiles, 1), dim3(256), 0, (const T *)partial, y, chunks, cols, cols, chunks,
                      kind, compat);
     sage_status st = ctx.check_cuda(cudaGetLastError(), "reduce_cols launch");
     ctx.allocator().free(scratch);  // stream-ordered: reused only by work enqueued after the second stage
