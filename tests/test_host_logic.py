@@ -393,7 +393,7 @@ def test_allocator_garbage_collects_old_cached_segments():
     held += [c.alloc(20 * MiB) for _ in range(7)]   # none of the cached segments fits: the pool grows to 242 MiB
     assert c.mem_stats()["mem_used"] == 200 * MiB and c.mem_stats()["mem_total"] == 242 * MiB
     r, runs, total = gc()
-    # 80 % in use.  Round 1 frees what is at least of average age (the old 12 MiB segment), round 2 the two
+    # 80 % in use.  The first pass frees what is at least of average age (the old 12 MiB segment), the second the two
     # younger ones; 42 < 50 MiB, but nothing is left
     assert r == (12 + 14 + 16) * MiB and runs == 1 and total == r
     assert c.mem_stats()["mem_total"] == 200 * MiB
