@@ -407,3 +407,36 @@ def test_allocator_garbage_collects_old_cached_segments():
     for b in held:
         c.free(b)
     c.close()
+
+
+def test_bert_training_plan():
+    """One training step of Bert (4 layers here, base width) on a planning context: LayerNorm's backward pass and the
+    softmax backward pieces run as generated row programs between the GEMMs, weight gradients are cut into K
+    slices, and after the first step (which splits the weights once) no tf32 split pass is left: every GEMM
+    operand's planes are written by the kernel that produces it or kept up to date by the optimizer."""
+    layers = 4
+    model = S.Bert(num_layers=layers)
+    c = S.Context(-1)
+    for p in model.params():
+        c.set(p, np.zeros(p.extents, np.float32))
+    ids, mask, lab = c.var(np.zeros((32, 128), np.uint32)), c.var(np.ones((32, 128), np.float32)), c.var(np.zeros((32, 1), np.uint32))
+    loss = S.softmax_cross_entropy(model.pass_(ids, mask), lab).mean([0], False)
+    grads = S.grad_param(loss, model)
+    opt = S.Adam(1e-4)
+    opt.init(c)
+    counts = []
+    for step in range(2):
+        c.trace_begin()
+        c.eval(*grads.values(), loss)
+        opt.update(grads, c)
+        c.clear()
+        t = c.trace()
+        counts.append({k: t.count(k) for k in ("sage_row_program", "split_tf32", "gemm_tc_3xtf32", "adam_update", "layernorm_rows")})
+    first, steady = counts
+    # LayerNorm backward (2 per layer + the embedding's) and two softmax backward pieces per layer
+    assert steady["sage_row_program"] == first["sage_row_program"] == (2 * layers + 1) + 2 * layers
+    assert first["split_tf32"] == 6 * layers and steady["split_tf32"] == 0                              # the weights, once
+    assert steady["gemm_tc_3xtf32"] == 24 * layers and steady["layernorm_rows"] == 2 * layers + 1
+    d = c.describe()
+    assert "row_program[4096x768" in d and "row_program[49152x128" in d
+    c.close()
