@@ -87,8 +87,9 @@ void free_split(Context &ctx, SplitPlanes *s);
 size_t split_tf32_bytes(int rows, int cols, int batches);
 sage_status split_tf32_into(Context &ctx, const float *src, long long ld, long long batch_stride, int rows, int cols, int batches,
                             float *dst, SplitPlanes *out);
-// `a` / `b` are the splits of g.a / g.b (as stored); g.a / g.b themselves are not read.
-sage_status gemm_tcgen05_planes(Context &ctx, const GemmArgs &g, const SplitPlanes &a, const SplitPlanes &b);
+// `a` / `b` are the splits of g.a / g.b (as stored); g.a / g.b themselves are not read.  With `no_split_k` the
+// product runs as one pass over K whatever its shape, so neither the allocator nor a second kernel is reached.
+sage_status gemm_tcgen05_planes(Context &ctx, const GemmArgs &g, const SplitPlanes &a, const SplitPlanes &b, bool no_split_k = false);
 
 // ---- the general form of the tensor-core GEMM, used by the evaluator's fused GEMM operator.
 // A split operand as the tensor core reads it: `rows` x `cols` with cols contiguous, rows `ld` floats
@@ -133,6 +134,7 @@ struct TcGemm {
     std::string epilogue;    // C expression over x0 (the product) and x1..x3 (aux); empty = x0
     bool row_softmax = false;  // store softmax over each output row of the expression; needs n <= 256 (one tile per row)
     int force_bn = 0;          // tile width chosen by the caller (64 / 128 / 192 / 256); 0 = the launcher's own choice
+    bool no_split_k = false;   // never cut K into slices: the launch then needs no scratch from the allocator
 };
 bool gemm_tc_shape_ok(long long m, long long n, long long k, long long batch);
 sage_status gemm_tc_run(Context &ctx, const TcGemm &g);

@@ -12,6 +12,8 @@
 // Limits and rules
 //   * 2 * 4 bytes * (rows_a * pitch(cols_a) + rows_b * pitch(cols_b)) must fit in kScratchBytes,
 //     where pitch rounds the contiguous extent up to 4 floats; larger problems get SAGE_ERR_INVALID.
+//   * A long K is never cut into slices here (sage_gemm does that with allocator scratch), so for k >= 1024
+//     with few output tiles this entry point is slower than sage_gemm and its sum order differs from it.
 //   * The first call on a device looks up the device address of the array (cudaGetSymbolAddress,
 //     with that device current).  Make that first call before any stream capture begins.
 //   * All calls share the one array, and it keeps whatever the previous call left in it.  Nothing
@@ -61,7 +63,8 @@ extern "C" sage_status sage_gemm_noalloc(sage_ctx *ctx, int32_t trans_a, int32_t
     k::GemmArgs g{trans_a != 0, trans_b != 0, m, n, k, (const float *)a->ptr + a_off, lda, 0, (const float *)b->ptr + b_off, ldb, 0,
                   (float *)c->ptr + c_off, ldc, 0, 1};
     if (!k::gemm_tc_supported(g))
-        return C.fail(SAGE_ERR_UNSUPPORTED, "sage_gemm_noalloc: needs m >= 64, n >= 32, k >= 32 (the tensor-core path); use sage_gemm");
+        return C.fail(SAGE_ERR_UNSUPPORTED,
+                      "sage_gemm_noalloc: needs n >= 32, k >= 32 and m >= 64 (or m >= 16 with k >= 2048): the tensor-core path; use sage_gemm");
     const int a_rows = g.ta ? (int)k : (int)m, a_cols = g.ta ? (int)m : (int)k;
     const int b_rows = g.tb ? (int)n : (int)k, b_cols = g.tb ? (int)k : (int)n;
     const size_t a_bytes = k::split_tf32_bytes(a_rows, a_cols, 1), b_bytes = k::split_tf32_bytes(b_rows, b_cols, 1);
@@ -78,5 +81,7 @@ extern "C" sage_status sage_gemm_noalloc(sage_ctx *ctx, int32_t trans_a, int32_t
     if (st) return st;
     st = k::split_tf32_into(C, g.b, g.ldb, 0, b_rows, b_cols, 1, scratch + a_span / sizeof(float), &pb);
     if (st) return st;
-    return k::gemm_tcgen05_planes(C, g, pa, pb);
+    // One pass over K: sage_gemm may cut a long K into slices, which takes partial-product scratch from the
+    // allocator and a second kernel.  Neither is reachable from here.
+    return k::gemm_tcgen05_planes(C, g, pa, pb, /*no_split_k=*/true);
 }

@@ -56,6 +56,41 @@ def test_noalloc_gemm_matches_regular_entry_point_twice_in_a_row():
         ctx.close()
 
 
+def test_noalloc_gemm_with_a_long_k_stays_off_the_allocator():
+    """sage_gemm cuts a long K with few output tiles into slices whose partial products live in allocator
+    memory.  The no-allocation entry point must not: one pass over K, nothing taken from the pool (which is
+    empty here, so any request would reach cudaMalloc and show in num_device_allocs)."""
+    ctx = S.Context(0)
+    rng = np.random.default_rng(78)
+    try:
+        for ta, tb, m, n, k in [(0, 0, 576, 64, 6272), (0, 0, 128, 512, 4608), (0, 0, 512, 512, 2048), (0, 0, 64, 64, 8192)]:
+            a = rng.uniform(-1, 1, (k, m) if ta else (m, k)).astype(np.float32)
+            b = rng.uniform(-1, 1, (n, k) if tb else (k, n)).astype(np.float32)
+            A, B, C = ctx.tensor(a), ctx.tensor(b), ctx.empty((m, n))
+            ctx._ck(S.lib.sage_release_cached(ctx.h))  # leave nothing in the pool that a hidden request could be served from
+            held = ctx.mem_stats()
+            outs = []
+            for _ in range(2):
+                ctx._ck(S.lib.sage_gemm_noalloc(ctx.h, ta, tb, L(m), L(n), L(k), A.buf, L(0), L(a.shape[1]), B.buf, L(0), L(b.shape[1]),
+                                                C.buf, L(0), L(n)))
+                outs.append(C.numpy())
+            after = ctx.mem_stats()
+            for key in ("mem_total", "mem_used", "mem_peak", "num_device_allocs"):
+                assert after[key] == held[key], (key, m, n, k)
+            assert np.array_equal(outs[0], outs[1])
+            for t in (A, B, C):
+                t.release()
+            # sage_gemm splits K for these shapes, so the sums differ in order: compare within the contraction tolerance
+            ref = gemm(ctx, S.lib.sage_gemm, ta, tb, m, n, k, a, b)
+            exact = a.astype(np.float64) @ b.astype(np.float64)
+            scale = np.maximum(np.abs(exact), np.sqrt(np.mean(exact * exact)))
+            assert np.max(np.abs(outs[0] - ref) / scale) <= 1e-4
+            assert np.max(np.abs(outs[0] - exact) / scale) <= 1e-5
+        assert ctx.status_word() == 0
+    finally:
+        ctx.close()
+
+
 def test_noalloc_gemm_rejects_what_does_not_fit():
     ctx = S.Context(0)
     try:
