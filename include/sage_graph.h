@@ -157,6 +157,9 @@ sage_status sage_bert_pass(sage_bert *b, const sage_var *token_ids, const sage_v
 
 /* ResNet::new(ResNetConfig::d18(chan_input, num_classes)) — src/models/resnet.rs:20-28,74-104 */
 sage_status sage_resnet18_create(int64_t chan_input, int64_t num_classes, sage_model **out);
+/* The same graph with the BatchNorm2d layers the reference has commented out (resnet.rs:80,167,170; layer:
+ * src/layers.rs:479-546) put back: inference normalisation by running statistics, eps 1e-05. */
+sage_status sage_resnet18_bn_create(int64_t chan_input, int64_t num_classes, sage_model **out);
 /* DenseNet::new(DenseNetConfig::d121 / d169 / d201(chan_input, num_classes)) — src/models/densenet.rs:20-107:
  * (depth, growth_rate) = (121, 12), (169, 24), (201, 12) */
 sage_status sage_densenet_create(int64_t chan_input, int64_t num_classes, int64_t depth, int64_t growth_rate, sage_model **out);
@@ -164,6 +167,9 @@ sage_status sage_densenet_create(int64_t chan_input, int64_t num_classes, int64_
 sage_status sage_mobilenet_v2_create(int64_t chan_in, int64_t num_classes, sage_model **out);
 sage_status sage_model_destroy(sage_model *m);
 sage_status sage_model_params(sage_model *m, sage_var **out, int32_t cap, int32_t *count);
+/* State that Parameter::params does not list: BatchNorm2d's running_mean / running_var (layers.rs:486-490), in
+ * traversal order.  Same calling convention as sage_model_params. */
+sage_status sage_model_buffers(sage_model *m, sage_var **out, int32_t cap, int32_t *count);
 sage_status sage_model_pass(sage_model *m, const sage_var *x, sage_var **out); /* Layer::pass, resnet.rs:138-142 */
 
 #ifdef __cplusplus

@@ -1002,6 +1002,16 @@ class LayerNorm:  # layers.rs:548-590: eps argument is ignored, 1e-05 is hard-co
     def __call__(self, x): return layer_norm(x, self.axes, self.gamma, self.beta, self.eps)
 
 
+class BatchNorm2d:  # layers.rs:479-546: params are gamma, beta ([1] each); pass() hard-codes eps 1e-05
+    def __init__(self, num_features, eps=1e-05):
+        self.gamma, self.beta = Var.empty([1]), Var.empty([1])
+        self.running_mean, self.running_var = Var.empty([num_features]), Var.empty([num_features])
+
+    def params(self): return [self.gamma, self.beta]
+    def buffers(self): return [self.running_mean, self.running_var]
+    def __call__(self, x): return batch_norm_2d(x, self.gamma, self.beta, self.running_mean, self.running_var, 1e-05)
+
+
 class Relu:
     def params(self): return []
     def __call__(self, x): return relu(x)
@@ -1039,6 +1049,7 @@ class Sequential:  # layers.rs:275-325
     def __init__(self, *layers): self.layers = list(layers)
     def add(self, l): self.layers.append(l); return self
     def params(self): return [p for l in self.layers for p in l.params()]
+    def buffers(self): return [p for l in self.layers for p in (l.buffers() if hasattr(l, "buffers") else [])]
 
     def __call__(self, x):
         for l in self.layers:
@@ -1120,25 +1131,34 @@ class Bert:  # models/bert.rs:57-139
 
 
 class BasicLayer:  # models/resnet.rs:150-177, 270-279
-    def __init__(self, cin, planes, stride):
-        self.main = Sequential(Conv2d(cin, planes, 3, stride, 1, 1), Relu(), Conv2d(planes, planes, 3, 1, 1, 1))
+    def __init__(self, cin, planes, stride, batch_norm=False):
+        if batch_norm:  # the two BatchNorm2d lines the reference has commented out (resnet.rs:167,170)
+            self.main = Sequential(Conv2d(cin, planes, 3, stride, 1, 1), BatchNorm2d(planes), Relu(),
+                                   Conv2d(planes, planes, 3, 1, 1, 1), BatchNorm2d(planes))
+        else:
+            self.main = Sequential(Conv2d(cin, planes, 3, stride, 1, 1), Relu(), Conv2d(planes, planes, 3, 1, 1, 1))
         self.down = Sequential(Conv2d(cin, planes, 1, stride, 0, 1)) if (stride != 1 or cin != planes) else None
 
     def params(self): return self.main.params() + (self.down.params() if self.down else [])
+    def buffers(self): return self.main.buffers() + (self.down.buffers() if self.down else [])
 
     def __call__(self, x):
         y = self.main(x)
         return relu(y + (self.down(x) if self.down else x))
 
 
-def resnet18(chan_input, num_classes):  # models/resnet.rs:74-129 with d18; BatchNorm is absent in the reference
-    m = Sequential(Conv2d(chan_input, 64, 7, 2, 3, 1), Relu(), MaxPool2d(3, 2, 1, 1))
+def resnet18(chan_input, num_classes, batch_norm=False):  # models/resnet.rs:74-129 with d18
+    # BatchNorm is commented out in the reference (:80, :167, :170); batch_norm=True puts it back at those places
+    m = Sequential(Conv2d(chan_input, 64, 7, 2, 3, 1))
+    if batch_norm:
+        m.add(BatchNorm2d(64))
+    m.add(Relu()).add(MaxPool2d(3, 2, 1, 1))
     cin, cout = 64, 64
     for i in range(4):
         stride = 1 if i == 0 else 2
         blk, c = Sequential(), cin
         for j in range(2):
-            blk.add(BasicLayer(c, cout, stride if j == 0 else 1))
+            blk.add(BasicLayer(c, cout, stride if j == 0 else 1, batch_norm))
             c = cout
         m.add(blk)
         cin, cout = cout, cout * 2

@@ -696,9 +696,19 @@ class MobileNetV2(_SequentialModel):
 class ResNet18:
     """ResNet::new(ResNetConfig::d18(chan_input, num_classes)) (src/models/resnet.rs:74-104)."""
 
-    def __init__(self, chan_input, num_classes):
+    def __init__(self, chan_input, num_classes, batch_norm=False):
+        """batch_norm=True puts back the BatchNorm2d layers (src/layers.rs:479-546) that the reference has
+        commented out at resnet.rs:80,167,170; their running statistics are `buffers()`."""
         self.h = _P()
-        _gck(lib.sage_resnet18_create(ctypes.c_int64(chan_input), ctypes.c_int64(num_classes), ctypes.byref(self.h)))
+        create = lib.sage_resnet18_bn_create if batch_norm else lib.sage_resnet18_create
+        _gck(create(ctypes.c_int64(chan_input), ctypes.c_int64(num_classes), ctypes.byref(self.h)))
+
+    def buffers(self):
+        n = ctypes.c_int32(0)
+        lib.sage_model_buffers(self.h, None, 0, ctypes.byref(n))
+        out = (_P * max(n.value, 1))()
+        lib.sage_model_buffers(self.h, out, n.value, ctypes.byref(n))
+        return [Var(_P(out[i])) for i in range(n.value)]
 
     def __del__(self):
         try:

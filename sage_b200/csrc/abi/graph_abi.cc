@@ -429,6 +429,12 @@ sage_status sage_resnet18_create(int64_t chan_input, int64_t num_classes, sage_m
         return SAGE_OK;
     });
 }
+sage_status sage_resnet18_bn_create(int64_t chan_input, int64_t num_classes, sage_model **out) {
+    return guarded([&]() -> sage_status {
+        *out = new sage_model{nn::resnet18(chan_input, num_classes, true)};
+        return SAGE_OK;
+    });
+}
 sage_status sage_densenet_create(int64_t chan_input, int64_t num_classes, int64_t depth, int64_t growth_rate, sage_model **out) {
     return guarded([&]() -> sage_status {
         *out = new sage_model{nn::densenet(chan_input, num_classes, depth, growth_rate)};
@@ -448,6 +454,11 @@ sage_status sage_model_destroy(sage_model *m) {
 sage_status sage_model_params(sage_model *m, sage_var **out, int32_t cap, int32_t *count) {
     std::vector<Var> p;
     m->impl->params(&p);
+    return fill_params(p, out, cap, count);
+}
+sage_status sage_model_buffers(sage_model *m, sage_var **out, int32_t cap, int32_t *count) {
+    std::vector<Var> p;
+    m->impl->buffers(&p);
     return fill_params(p, out, cap, count);
 }
 sage_status sage_model_pass(sage_model *m, const sage_var *x, sage_var **out) { OP(m->impl->pass(x->v)); }

@@ -25,6 +25,7 @@ struct GemmP {
     long long ldb, sb;
     float *c;
     long long ldc, sc;
+    long long tiles_n, tiles_m, batch;  // the grid is one-dimensional: block = (batch * tiles_m + tile_m) * tiles_n + tile_n
 };
 
 template <bool TA, bool TB>
@@ -32,10 +33,14 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(GemmP p) {
     __shared__ __align__(16) float As[BK][BM];
     __shared__ __align__(16) float Bs[BK][BN];
     const int t = threadIdx.x;
-    const long long m0 = (long long)blockIdx.y * BM, n0 = (long long)blockIdx.x * BN;
-    const float *A = p.a + (long long)blockIdx.z * p.sa;
-    const float *B = p.b + (long long)blockIdx.z * p.sb;
-    float *C = p.c + (long long)blockIdx.z * p.sc;
+    // a one-dimensional grid: the y / z extents of a grid stop at 65535, which many small batches or a very tall
+    // M would exceed
+    const long long tile_n = blockIdx.x % p.tiles_n, rest = blockIdx.x / p.tiles_n;
+    const long long tile_m = rest % p.tiles_m, bz = rest / p.tiles_m;
+    const long long m0 = tile_m * BM, n0 = tile_n * BN;
+    const float *A = p.a + bz * p.sa;
+    const float *B = p.b + bz * p.sb;
+    float *C = p.c + bz * p.sc;
     const int tx = t % 16, ty = t / 16;
     float acc[8][8];
 #pragma unroll
@@ -113,30 +118,31 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(GemmP p, long long sai
     const int lane = threadIdx.x & 31;
     const long long out = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const long long per_batch = p.m * p.n;
-    if (out >= per_batch * (long long)gridDim.y) return;
-    const long long i = out / p.n, j = out % p.n;
-    const float *A = p.a + (long long)blockIdx.y * p.sa + i * sai;
-    const float *B = p.b + (long long)blockIdx.y * p.sb + j * sbj;
+    if (out >= per_batch * p.batch) return;
+    const long long bz = out / per_batch, rem = out % per_batch;
+    const long long i = rem / p.n, j = rem % p.n;
+    const float *A = p.a + bz * p.sa + i * sai;
+    const float *B = p.b + bz * p.sb + j * sbj;
     float acc = 0.f;
     for (long long kk = lane; kk < p.k; kk += 32) acc = fmaf(A[kk * sak], B[kk * sbk], acc);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    if (lane == 0 && out < per_batch) p.c[(long long)blockIdx.y * p.sc + i * p.ldc + j] = acc;
+    if (lane == 0) p.c[bz * p.sc + i * p.ldc + j] = acc;
 }
 }  // namespace
 
 sage_status gemm_simt(Context &ctx, const GemmArgs &g) {
     ctx.note_launch("gemm_simt");
     if (ctx.dry() || g.m == 0 || g.n == 0 || g.batch == 0) return SAGE_OK;
-    if (g.m * g.n <= 8192 && g.k >= 128 && g.batch <= 65535) {
-        GemmP p{g.m, g.n, g.k, g.a, g.lda, g.stride_a, g.b, g.ldb, g.stride_b, g.c, g.ldc, g.stride_c};
-        const dim3 grid((unsigned)((g.m * g.n + 7) / 8), (unsigned)g.batch);
+    GemmP p{g.m, g.n, g.k, g.a, g.lda, g.stride_a, g.b, g.ldb, g.stride_b, g.c, g.ldc, g.stride_c, (g.n + BN - 1) / BN, (g.m + BM - 1) / BM, g.batch};
+    const long long grid_limit = 0x7fffffffLL;
+    if (g.m * g.n <= 8192 && g.k >= 128 && (g.m * g.n * g.batch + 7) / 8 <= grid_limit) {
+        const dim3 grid((unsigned)((g.m * g.n * g.batch + 7) / 8));
         gemm_skinny_kernel<<<grid, 256, 0, ctx.stream()>>>(p, g.ta ? 1 : g.lda, g.ta ? g.lda : 1, g.tb ? 1 : g.ldb, g.tb ? g.ldb : 1);
         return ctx.check_cuda(cudaGetLastError(), "gemm_skinny launch");
     }
-    GemmP p{g.m, g.n, g.k, g.a, g.lda, g.stride_a, g.b, g.ldb, g.stride_b, g.c, g.ldc, g.stride_c};
-    dim3 grid((unsigned)((g.n + BN - 1) / BN), (unsigned)((g.m + BM - 1) / BM), (unsigned)g.batch);
-    if (grid.y > 65535 || grid.z > 65535) return ctx.fail(SAGE_ERR_UNSUPPORTED, "gemm_simt: grid too large");
+    if (p.tiles_n * p.tiles_m > grid_limit / g.batch) return ctx.fail(SAGE_ERR_UNSUPPORTED, "gemm_simt: more than 2^31 tiles");
+    const dim3 grid((unsigned)(p.tiles_n * p.tiles_m * g.batch));
     cudaStream_t s = ctx.stream();
     if (!g.ta && !g.tb) gemm_simt_kernel<false, false><<<grid, 256, 0, s>>>(p);
     else if (!g.ta && g.tb) gemm_simt_kernel<false, true><<<grid, 256, 0, s>>>(p);

@@ -52,6 +52,24 @@ void LayerNorm::params(std::vector<Var> *p) const {
     p->push_back(beta);
 }
 
+BatchNorm2d::BatchNorm2d(long long n, float e)
+    : eps(e), gamma(Var::empty({1}, SAGE_F32)), beta(Var::empty({1}, SAGE_F32)), running_mean(Var::empty({n}, SAGE_F32)),
+      running_var(Var::empty({n}, SAGE_F32)) {
+    gamma.origin->name = "batch_norm_2d.gamma";
+    beta.origin->name = "batch_norm_2d.beta";
+    running_mean.origin->name = "batch_norm_2d.running_mean";
+    running_var.origin->name = "batch_norm_2d.running_var";
+}
+Var BatchNorm2d::pass(const Var &x) const { return batch_norm_2d(x, gamma, beta, running_mean, running_var, 1e-05f); }  // layers.rs:535-545
+void BatchNorm2d::params(std::vector<Var> *p) const {
+    p->push_back(gamma);
+    p->push_back(beta);
+}
+void BatchNorm2d::buffers(std::vector<Var> *p) const {
+    p->push_back(running_mean);
+    p->push_back(running_var);
+}
+
 Var Gelu::pass(const Var &x) const {
     Var e = unary_map(div(x, std::sqrt(2.0f)), Erf);
     return mul(mul(x, 0.5f), add(e, 1.0f));
@@ -71,6 +89,9 @@ Var Sequential::pass(const Var &x0) const {
 }
 void Sequential::params(std::vector<Var> *p) const {
     for (auto &l : layers) l->params(p);
+}
+void Sequential::buffers(std::vector<Var> *p) const {
+    for (auto &l : layers) l->buffers(p);
 }
 
 // ---------------------------------------------------------------- Bert (models/bert.rs)
@@ -143,11 +164,13 @@ void Bert::params(std::vector<Var> *p) const {
 struct BasicLayer : Layer {  // resnet.rs:150-177, 270-279
     Sequential main;
     std::shared_ptr<Sequential> down;
-    BasicLayer(long long cin, long long planes, long long stride) {
+    BasicLayer(long long cin, long long planes, long long stride, bool batch_norm) {
         auto P = [](long long v) { return Pair{v, v}; };
         main.add(std::make_shared<Conv2d>(cin, planes, P(3), P(stride), P(1), P(1)));
+        if (batch_norm) main.add(std::make_shared<BatchNorm2d>(planes, 1e-05f));  // resnet.rs:167
         main.add(std::make_shared<Relu>());
         main.add(std::make_shared<Conv2d>(planes, planes, P(3), P(1), P(1), P(1)));
+        if (batch_norm) main.add(std::make_shared<BatchNorm2d>(planes, 1e-05f));  // resnet.rs:170
         if (stride != 1 || cin != planes) {
             down = std::make_shared<Sequential>();
             down->add(std::make_shared<Conv2d>(cin, planes, P(1), P(stride), P(0), P(1)));
@@ -161,12 +184,17 @@ struct BasicLayer : Layer {  // resnet.rs:150-177, 270-279
         main.params(p);
         if (down) down->params(p);
     }
+    void buffers(std::vector<Var> *p) const override {
+        main.buffers(p);
+        if (down) down->buffers(p);
+    }
 };
 
-std::shared_ptr<Sequential> resnet18(long long chan_input, long long num_classes) {
+std::shared_ptr<Sequential> resnet18(long long chan_input, long long num_classes, bool batch_norm) {
     auto P = [](long long v) { return Pair{v, v}; };
     auto m = std::make_shared<Sequential>();
     m->add(std::make_shared<Conv2d>(chan_input, 64, P(7), P(2), P(3), P(1)));
+    if (batch_norm) m->add(std::make_shared<BatchNorm2d>(64, 1e-05f));  // resnet.rs:80
     m->add(std::make_shared<Relu>());
     m->add(std::make_shared<MaxPool2d>(P(3), P(2), P(1), P(1)));
     long long cin = 64, cout = 64;
@@ -175,7 +203,7 @@ std::shared_ptr<Sequential> resnet18(long long chan_input, long long num_classes
         auto blk = std::make_shared<Sequential>();
         long long c = cin;
         for (int j = 0; j < 2; ++j) {
-            blk->add(std::make_shared<BasicLayer>(c, cout, j == 0 ? stride : 1));
+            blk->add(std::make_shared<BasicLayer>(c, cout, j == 0 ? stride : 1, batch_norm));
             c = cout;
         }
         m->add(blk);

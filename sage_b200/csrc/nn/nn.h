@@ -14,6 +14,7 @@ struct Layer {
     virtual ~Layer() {}
     virtual Var pass(const Var &x) const = 0;
     virtual void params(std::vector<Var> *p) const {}
+    virtual void buffers(std::vector<Var> *p) const {}  // state that is not a parameter (BatchNorm2d's running statistics)
 };
 
 struct Dense : Layer {
@@ -46,6 +47,18 @@ struct LayerNorm : Layer {
     LayerNorm(const std::vector<long long> &axes, float eps);
     Var pass(const Var &x) const override;
     void params(std::vector<Var> *p) const override;
+};
+
+// layers.rs:479-546: inference-mode normalisation with running statistics per channel; gamma / beta are [1]
+// tensors; the layer always passes eps = 1e-05 (layers.rs:542) whatever it was constructed with.
+// Only gamma and beta are parameters (layers.rs:528-531); the running statistics are `buffers`.
+struct BatchNorm2d : Layer {
+    float eps;
+    Var gamma, beta, running_mean, running_var;
+    BatchNorm2d(long long num_features, float eps);
+    Var pass(const Var &x) const override;
+    void params(std::vector<Var> *p) const override;
+    void buffers(std::vector<Var> *p) const override;
 };
 
 struct Softmax : Layer {  // layers.rs:249-273
@@ -85,6 +98,7 @@ struct Sequential : Layer {
     }
     Var pass(const Var &x) const override;
     void params(std::vector<Var> *p) const override;
+    void buffers(std::vector<Var> *p) const override;
 };
 
 // models/bert.rs:8-55.  `base()` is the reference's constructor; the other fields let the harness
@@ -124,8 +138,10 @@ struct Bert {
     void params(std::vector<Var> *p) const;                 // bert.rs:90-94 traversal order
 };
 
-// models/resnet.rs:74-129 with ResNetConfig::d18 (BatchNorm is commented out in the reference).
-std::shared_ptr<Sequential> resnet18(long long chan_input, long long num_classes);
+// models/resnet.rs:74-129 with ResNetConfig::d18.  BatchNorm is commented out in the reference (:80, :167, :170);
+// `batch_norm` puts a BatchNorm2d back at exactly those three places (after the first convolution and after
+// both convolutions of every BasicLayer), which is the inference-BatchNorm variant of the workload.
+std::shared_ptr<Sequential> resnet18(long long chan_input, long long num_classes, bool batch_norm = false);
 // models/densenet.rs:56-107: DenseNetConfig::d121 / d169 / d201 are (depth, growth rate) = (121, 12), (169, 24), (201, 12);
 // BatchNorm and dropout are declared in the reference's config but never applied.
 std::shared_ptr<Sequential> densenet(long long chan_input, long long num_classes, long long depth, long long growth_rate);

@@ -1,4 +1,4 @@
-"""BASELINE configs 4 and 5 at their full sizes.  The CPU oracle cannot evaluate them in reasonable
+"""BASELINE configs 3, 4 and 5 at their full sizes.  The CPU oracle cannot evaluate them in reasonable
 time, so the full batch is checked through properties that do not depend on size:
 
   * a forward pass is independent per sample: the first rows of the full-batch result must equal the
@@ -8,6 +8,8 @@ time, so the full batch is checked through properties that do not depend on size
   * shuffling the batch shuffles the outputs (again bit for bit);
   * the small batch itself is compared with the oracle (rel <= 1e-3 on logits).
 
+Config 3 is sage's Bert base graph at batch 32 x 128 tokens (the benchmarked workload: at this batch the
+projections take other tile widths, the grouped Q / K / V launch and the fused attention kernel's full grid).
 Config 4 is the BERT-large-shaped graph (24 layers, width 1024, 16 heads, FFN 4096, L 512, batch 256,
 ragged padding 0-128 per sequence); config 5 is sage's ResNet-18 graph on [256, 224, 224, 3].
 Weights and inputs are seeded synthetic tensors with the distributions BASELINE.json states.
@@ -34,6 +36,46 @@ def RV(a, dtype=None):
 
 
 LARGE = dict(embed_dim=1024, num_vocabs=30522, max_num_tokens=512, hidden_dim=4096, num_layers=24, num_heads=16, num_classes=2)
+
+
+@pytest.mark.parametrize("pad", [False, True])
+def test_config3_bert_base_full_batch(pad):
+    """pad=False is BASELINE config 3 as stated (mask all ones); pad=True adds ragged padding so that the additive
+    mask is exercised at the benchmarked batch too."""
+    rng = np.random.default_rng(3001)
+    batch, seq = 32, 128
+    ctx = S.Context(0)
+    try:
+        model = S.Bert()
+        params = model.params()
+        values = [(rng.standard_normal(p.extents) * 0.02).astype(np.float32) for p in params]
+        for p, v in zip(params, values):
+            ctx.set(p, v)
+        ids = rng.integers(0, 30522, (batch, seq)).astype(np.uint32)
+        mask = np.ones((batch, seq), np.float32)
+        if pad:
+            for i, n in enumerate(rng.integers(0, 33, batch)):
+                mask[i, seq - n:] = 0
+
+        def run(rows):
+            return model.pass_(ctx.var(ids[rows]), ctx.var(mask[rows])).eval(ctx)
+        full = run(np.arange(batch))
+        assert full.shape == (batch, 2) and np.isfinite(full).all() and np.array_equal(full, run(np.arange(batch)))
+        small = run(np.arange(2))
+        # per-sample independence, to fp32 rounding: at 2 sequences the projections are cut into K slices
+        rms = float(np.sqrt((full.astype(np.float64) ** 2).mean()))
+        assert float(np.abs(small - full[:2]).max()) / rms <= 1e-5
+        perm = rng.permutation(batch)
+        assert np.array_equal(run(perm), full[perm])                # batch order does not matter, bit for bit
+        assert ctx.status_word() == 0
+        rm = R.Bert(R.BertConfig())
+        for p, v in zip(rm.params(), values):
+            p.set(v)
+        ref = rm(RV(ids[:2], R.UINT), RV(mask[:2])).eval().numpy()
+        assert rel_err(small, ref, floor=1e-3) <= 1e-3
+        assert rel_err(full[:2], ref, floor=1e-3) <= 1e-3          # the batch-32 rows themselves against the oracle
+    finally:
+        ctx.close()
 
 
 def test_config4_bert_large_full_batch():

@@ -15,6 +15,7 @@ import pytest
 
 import sage_b200 as S
 from oracle import sage_ref as R
+from parity_metrics import check_envelope
 
 pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
@@ -147,6 +148,77 @@ def test_binary_logic_casts_exact(ctx):
     u = rng.integers(0, 2, (1000,)).astype(np.uint32)
     gf = ctx.var(u).float().eval(ctx)
     assert gf.dtype == np.float32 and np.array_equal(gf, u.astype(np.float32))
+
+
+def test_div_mod_pow_and_logic_vs_oracle(ctx):
+    """The binary / unary maps of src/ops/map.rs:224-302 that have no other value test: `/`, `mod`, `pow`,
+    `&&`, `||`, `!`.  Logic results are uint and bit-exact, also on float operands (C truthiness: non-zero is
+    true, so -0.0 is false and NaN is true); div is one correctly rounded division: bit-exact; fmod is exact by
+    definition; pow goes through the device's powf: rel <= 1e-4."""
+    rng = np.random.default_rng(81)
+    a = rng.uniform(-4, 4, (37, 129)).astype(np.float32)
+    b = rng.uniform(0.25, 4, (37, 129)).astype(np.float32) * np.where(rng.random((37, 129)) < 0.5, -1, 1).astype(np.float32)
+    va, vb = ctx.var(a), ctx.var(b)
+    got = S.div(va, vb).eval(ctx)
+    assert got.dtype == np.float32 and np.array_equal(got, R.div(RV(a), RV(b)).eval().numpy())
+    got = S.modular(va, vb).eval(ctx)
+    assert np.array_equal(got, R.modular(RV(a), RV(b)).eval().numpy())
+    base = np.abs(a) + np.float32(0.05)
+    got = S.pow_(ctx.var(base), vb).eval(ctx)
+    assert rel_err(got, R.pow_(RV(base), RV(b)).eval().numpy()) <= 1e-4
+    # broadcast + scalar operand forms (into_var of a literal, map.rs:412-429)
+    row = rng.uniform(0.5, 2, (129,)).astype(np.float32)
+    assert np.array_equal((va / ctx.var(row)).eval(ctx), (RV(a) / RV(row)).eval().numpy())
+    assert np.array_equal((va / 3.0).eval(ctx), (RV(a) / 3.0).eval().numpy())
+    # logic on uint operands (the results of compares) and on floats with the awkward values
+    x = rng.integers(-2, 3, (33, 65)).astype(np.float32)
+    y = rng.integers(-2, 3, (33, 65)).astype(np.float32)
+    x[0, :4] = [0.0, -0.0, np.nan, 1e-30]
+    y[0, :4] = [1.0, 1.0, 0.0, -0.0]
+    vx, vy = ctx.var(x), ctx.var(y)
+    for name in ("and_", "or_"):
+        got = getattr(S, name)(vx, vy).eval(ctx)
+        ref = getattr(R, name)(RV(x), RV(y)).eval().numpy()
+        assert got.dtype == np.uint32 == ref.dtype and np.array_equal(got, ref), name
+        got = getattr(S, name)(S.gt(vx, 0.0), S.lt(vy, 1.0)).eval(ctx)
+        ref = getattr(R, name)(R.gt(RV(x), 0.0), R.lt(RV(y), 1.0)).eval().numpy()
+        assert got.dtype == np.uint32 and np.array_equal(got, ref), name
+    got = S.not_(vx).eval(ctx)
+    ref = R.not_(RV(x)).eval().numpy()
+    assert got.dtype == np.uint32 == ref.dtype and np.array_equal(got, ref)
+    assert np.array_equal(S.not_(S.ge(vx, vy)).eval(ctx), R.not_(R.ge(RV(x), RV(y))).eval().numpy())
+    # gradients of div and pow (map.rs:1014-1042) through the same kernels
+    vbase = ctx.var(base)
+    out = S.sum_(S.pow_(vbase, vb) / vb, [0, 1])
+    rbase, rb = RV(base), RV(b)
+    rout = R.sum_(R.pow_(rbase, rb) / rb, [0, 1])
+    g1, g2 = vbase.grad(out).eval(ctx), vb.grad(out).eval(ctx)
+    r1, r2 = [t.numpy() for t in R.evaluate([rbase.grad(rout), rb.grad(rout)])]
+    assert rel_err(g1, r1, floor=1e-5) <= 1e-4 and rel_err(g2, r2, floor=1e-5) <= 1e-4
+
+
+@pytest.mark.parametrize("shape", [(3, 9, 11, 16), (2, 5, 7, 3), (4, 8, 8, 64)])
+def test_batch_norm_2d_vs_oracle(ctx, shape):
+    """batch_norm_2d (src/ops/conv.rs:167-185): gamma * (x - mean) / sqrt(var + eps) + beta with per-channel running
+    statistics and [1] gamma / beta, as BatchNorm2d::pass builds it (src/layers.rs:535-545)."""
+    rng = np.random.default_rng(82)
+    c = shape[3]
+    x = rng.standard_normal(shape).astype(np.float32)
+    mean_ = rng.standard_normal((c,)).astype(np.float32)
+    var_ = rng.uniform(0.3, 2.0, (c,)).astype(np.float32)
+    for gamma, beta in ((np.float32([1.0]), np.float32([0.0])), (np.float32([0.7]), np.float32([-0.3])),
+                        (rng.uniform(0.5, 1.5, (c,)).astype(np.float32), rng.standard_normal((c,)).astype(np.float32))):
+        got = S.batch_norm_2d(ctx.var(x), ctx.var(gamma), ctx.var(beta), ctx.var(mean_), ctx.var(var_), 1e-5).eval(ctx)
+        ref = R.batch_norm_2d(RV(x), RV(gamma), RV(beta), RV(mean_), RV(var_), 1e-5).eval().numpy()
+        assert got.shape == ref.shape and rel_err(got, ref, floor=1e-4) <= 1e-4
+    xv = ctx.var(x)
+    g, b = ctx.var(np.float32([0.7])), ctx.var(np.float32([-0.3]))
+    out = S.sum_(S.square(S.batch_norm_2d(xv, g, b, ctx.var(mean_), ctx.var(var_), 1e-5)), [0, 1, 2, 3])
+    rx, rg, rb = RV(x), RV(np.float32([0.7])), RV(np.float32([-0.3]))
+    rout = R.sum_(R.square(R.batch_norm_2d(rx, rg, rb, RV(mean_), RV(var_), 1e-5)), [0, 1, 2, 3])
+    gx, gg = xv.grad(out).eval(ctx), g.grad(out).eval(ctx)
+    rgx, rgg = [t.numpy() for t in R.evaluate([rx.grad(rout), rg.grad(rout)])]
+    assert rel_err(gx, rgx, floor=1e-4) <= 1e-4 and rel_err(gg, rgg, floor=1e-4) <= 1e-4
 
 
 def test_broadcast_and_strided_views(ctx):
@@ -372,6 +444,8 @@ def test_matmul_vs_oracle(ctx, m, n, k):
     assert gemm_err(got, ref) <= 1e-4
     f64 = a.astype(np.float64) @ b.astype(np.float64)
     assert np.linalg.norm(got - f64) / max(np.linalg.norm(f64), 1e-30) <= 2e-6
+    # the strict elementwise metric against the envelope of the oracle's FMA / non-FMA sums
+    check_envelope("matmul %dx%dx%d" % (m, n, k), got, lambda: R.matmul(RV(a), RV(b)).eval().numpy(), f64)
 
 
 @pytest.mark.parametrize("m,n,k", [(200, 136, 72), (320, 72, 4480)])  # the second: few tiles, long K, split over K
@@ -383,6 +457,8 @@ def test_gemm_transposes_vs_oracle(ctx, ta, tb, m, n, k):
     got = S.gemm(ctx.var(a), ctx.var(b), ta, tb).eval(ctx)
     ref = R.gemm(RV(a), RV(b), bool(ta), bool(tb)).eval().numpy()
     assert gemm_err(got, ref) <= 1e-4
+    f64 = (a.T if ta else a).astype(np.float64) @ (b.T if tb else b).astype(np.float64)
+    check_envelope("gemm t%d%d %dx%dx%d" % (ta, tb, m, n, k), got, lambda: R.gemm(RV(a), RV(b), bool(ta), bool(tb)).eval().numpy(), f64)
 
 
 @pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
@@ -397,6 +473,8 @@ def test_skinny_gemm_vs_oracle(ctx, ta, tb):
     assert "gemm_simt" in ctx.trace()
     ref = R.gemm(RV(a), RV(b), bool(ta), bool(tb)).eval().numpy()
     assert gemm_err(got, ref) <= 1e-4
+    f64 = (a.T if ta else a).astype(np.float64) @ (b.T if tb else b).astype(np.float64)
+    check_envelope("skinny gemm t%d%d" % (ta, tb), got, lambda: R.gemm(RV(a), RV(b), bool(ta), bool(tb)).eval().numpy(), f64)
     a3 = rng.uniform(-1, 1, (5, 8, 300)).astype(np.float32)
     b3 = rng.uniform(-1, 1, (5, 300, 2)).astype(np.float32)
     got = S.matmul_batched(ctx.var(a3), ctx.var(b3)).eval(ctx)
@@ -411,6 +489,8 @@ def test_batch_matmul_vs_oracle(ctx, sa, sb):
     got = S.matmul_batched(ctx.var(a), ctx.var(b)).eval(ctx)
     ref = R.matmul_batched(RV(a), RV(b)).eval().numpy()
     assert gemm_err(got, ref) <= 1e-4
+    check_envelope("matmul_batched %s x %s" % (sa, sb), got, lambda: R.matmul_batched(RV(a), RV(b)).eval().numpy(),
+                   a.astype(np.float64) @ b.astype(np.float64))
 
 
 @pytest.mark.parametrize("n", [4096, 8192])
@@ -449,6 +529,10 @@ def test_conv_pool_vs_oracle(ctx):
         got = S.conv_2d(ctx.var(x), ctx.var(f), stride, pad, 1).eval(ctx)
         ref = R.conv_2d(RV(x), RV(f), stride, pad, 1).eval().numpy()
         assert gemm_err(got, ref) <= 1e-4
+        cols = R.im2col(RV(x), [3, 3], stride, pad, 1).eval().numpy().astype(np.float64)
+        f64 = cols.reshape(-1, 45) @ f.astype(np.float64).reshape(45, 8)
+        check_envelope("conv_2d stride %d pad %d" % (stride, pad), got.reshape(-1, 8),
+                       lambda: R.conv_2d(RV(x), RV(f), stride, pad, 1).eval().numpy().reshape(-1, 8), f64)
     got = S.max_pool_2d(ctx.var(x), 3, 2, 1, 1).eval(ctx)
     assert np.array_equal(got, R.max_pool_2d(RV(x), 3, 2, 1, 1).eval().numpy())
     got = S.avg_pool_2d(ctx.var(x), [19, 17], [19, 17], 0, 1).eval(ctx)
@@ -527,9 +611,22 @@ def test_bert_base_vs_oracle(ctx):
     assert got.shape == (2, 2) and rel_err(got, ref, floor=1e-3) <= 1e-3
 
 
-def test_resnet18_vs_oracle(ctx):
+def test_bert_base_gelu_eps_variant_vs_oracle(ctx):
+    """The extra variant of BASELINE config 3: erf-GELU feed-forward and LayerNorm eps 1e-12 at base width
+    (12 layers, 768, 12 heads, FFN 3072), seq 128, batch 2, the same seeded weights as the ReLU test."""
+    cfg = dict(gelu=1, layer_norm_eps=1e-12)
+    got, ref = run_bert(ctx, cfg, batch=2, seq=128, seed=3001, gelu=True, ln_eps=1e-12)
+    assert got.shape == (2, 2) and rel_err(got, ref, floor=1e-3) <= 1e-3
+    ctx.clear()
+
+
+@pytest.mark.parametrize("batch_norm", [False, True])
+def test_resnet18_vs_oracle(ctx, batch_norm):
+    """batch_norm=True: the extra variant of BASELINE config 5 — inference BatchNorm after every convolution where
+    the reference has it commented out (src/models/resnet.rs:80,167,170), running mean 0 / variance 1, gamma 1,
+    beta 0, eps 1e-5; a second pass uses non-trivial statistics so that the normalisation really acts."""
     rng = np.random.default_rng(5002)
-    model = S.ResNet18(3, 10)
+    model = S.ResNet18(3, 10, batch_norm=batch_norm)
     params = model.params()
     values = []
     for p in params:
@@ -540,17 +637,35 @@ def test_resnet18_vs_oracle(ctx):
             values.append((rng.standard_normal(p.extents) * 0.02).astype(np.float32))
         else:
             values.append((rng.standard_normal(p.extents) * 0.01).astype(np.float32))
+    if batch_norm:  # gamma / beta are the only [1] parameters; set them by name order: gamma first
+        flip = 0
+        for i, p in enumerate(params):
+            if tuple(p.extents) == (1,):
+                values[i] = np.float32([1.0 if flip == 0 else 0.0])
+                flip ^= 1
     for p, v in zip(params, values):
         ctx.set(p, v)
     x = rng.standard_normal((2, 64, 64, 3)).astype(np.float32)
-    got = model.pass_(ctx.var(x)).eval(ctx)
-    rm = R.resnet18(3, 10)
+    rm = R.resnet18(3, 10, batch_norm)
     rp = rm.params()
     assert [tuple(p.extents) for p in rp] == [tuple(p.extents) for p in params]
     for p, v in zip(rp, values):
         p.set(v)
-    ref = rm(RV(x)).eval().numpy()
-    assert got.shape == (2, 10) and rel_err(got, ref, floor=1e-3) <= 1e-3
+    bufs, rbufs = model.buffers(), rm.buffers()
+    assert len(bufs) == len(rbufs) == (34 if batch_norm else 0)
+    for trial in range(2 if batch_norm else 1):
+        for i, (b, rb) in enumerate(zip(bufs, rbufs)):
+            if trial == 0:
+                v = np.zeros(b.extents, np.float32) if i % 2 == 0 else np.ones(b.extents, np.float32)
+            else:
+                v = (rng.standard_normal(b.extents) * 0.1 if i % 2 == 0 else rng.uniform(0.5, 1.5, b.extents)).astype(np.float32)
+            ctx.set(b, v)
+            rb.set(v)
+        ctx.clear()
+        got = model.pass_(ctx.var(x)).eval(ctx)
+        ref = rm(RV(x)).eval().numpy()
+        assert got.shape == (2, 10) and rel_err(got, ref, floor=1e-3) <= 1e-3
+    assert ctx.status_word() == 0
 
 
 # ------------------------------------------------------------------------------ runtime behaviour
