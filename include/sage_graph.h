@@ -60,6 +60,11 @@ sage_status sage_grad(const sage_var *y, sage_var *const *xs, int32_t n, sage_va
 /* One line per routine of the last compiled program: the fused kernels and what feeds them. */
 sage_status sage_session_describe(sage_session *s, char *out, size_t out_len, size_t *needed);
 sage_status sage_session_stats(sage_session *s, uint64_t *programs_compiled);
+/* Compiled programs are cached per (targets, evaluated inputs), at most `limit` of them, least recently used
+ * dropped first; a cached program keeps its graph's tensors alive.  The reference recompiles on every eval
+ * (src/session/context.rs:96-117) and keeps nothing, so it has no counterpart for these two. */
+sage_status sage_session_programs_cached(sage_session *s, uint64_t *count, uint64_t *limit);
+sage_status sage_session_drop_programs(sage_session *s);
 
 /* ---- map ops, src/ops/map.rs.  Kinds follow the reference's enums (UnaryMap :92-130, BinaryMap :151-172). */
 enum { SAGE_U_COPY, SAGE_U_ABS, SAGE_U_NEG, SAGE_U_RECIP, SAGE_U_LOG, SAGE_U_EXP, SAGE_U_SQRT, SAGE_U_SQUARE, SAGE_U_ERF,

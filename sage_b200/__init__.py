@@ -185,6 +185,15 @@ class Context:
         lib.sage_session_stats(self.s, ctypes.byref(n))
         return n.value
 
+    def programs_cached(self):
+        """(programs held by the session's cache, the cache's limit)."""
+        n, lim = ctypes.c_uint64(0), ctypes.c_uint64(0)
+        lib.sage_session_programs_cached(self.s, ctypes.byref(n), ctypes.byref(lim))
+        return n.value, lim.value
+
+    def drop_programs(self):
+        lib.sage_session_drop_programs(self.s)
+
     def mem_stats(self):
         m = MemStats()
         self._ck(lib.sage_mem_stats(self.h, ctypes.byref(m)))

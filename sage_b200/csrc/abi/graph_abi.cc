@@ -218,6 +218,15 @@ sage_status sage_session_stats(sage_session *s, uint64_t *programs_compiled) {
     *programs_compiled = s->impl->programs_compiled;
     return SAGE_OK;
 }
+sage_status sage_session_programs_cached(sage_session *s, uint64_t *count, uint64_t *limit) {
+    if (count) *count = s->impl->programs_cached();
+    if (limit) *limit = Session::kMaxPrograms;
+    return SAGE_OK;
+}
+sage_status sage_session_drop_programs(sage_session *s) {
+    s->impl->drop_programs();
+    return SAGE_OK;
+}
 
 // ---------------------------------------------------------------- ops
 #define OP(body) return guarded([&]() -> sage_status { return ret(out, body); })

@@ -190,10 +190,17 @@ public:
     // Kernel trace of the last compiled program, one routine per line (for tests / planning).
     std::string describe_last() const;
     uint64_t programs_compiled = 0;
+    // Compiled programs are kept, least recently used first, up to this many.  A cached program keeps its whole
+    // graph alive (leaf tensors, grouped weight copies, tf32 planes, generated kernels), so a loop that builds a
+    // fresh graph per step would otherwise grow without bound; the reference recompiles on every eval
+    // (context.rs:96-117) and keeps nothing.
+    static constexpr size_t kMaxPrograms = 32;
+    size_t programs_cached() const { return cache_.size(); }
+    void drop_programs();  // forget every compiled program (and what it holds alive)
 
 private:
     Context *ctx_;
-    std::vector<std::unique_ptr<Program>> cache_;
+    std::vector<std::unique_ptr<Program>> cache_;  // least recently used first
     Program *last_ = nullptr;
 };
 

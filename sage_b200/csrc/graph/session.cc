@@ -100,6 +100,7 @@ struct Routine {
 
 struct Program {
     std::vector<Origin *> target_keys, x_keys;
+    uint64_t key_hash = 0;  // of (target_keys, x_keys): compared before the lists
     std::vector<Var> outputs;
     std::unordered_map<Origin *, Routine> routines;
     std::unordered_map<Origin *, int> consumers;  // how many routines read each state
@@ -111,6 +112,26 @@ Session::Session(Context *ctx) : ctx_(ctx) {}
 Session::~Session() {}
 
 void Session::clear() { data.clear(); }
+
+void Session::drop_programs() {
+    last_ = nullptr;
+    cache_.clear();
+}
+
+static uint64_t program_key_hash(const std::vector<Origin *> &targets, const std::vector<Origin *> &inputs) {
+    uint64_t h = 0xcbf29ce484222325ull;  // FNV-1a over the two pointer lists and their lengths
+    auto mix = [&](uint64_t v) {
+        for (int i = 0; i < 8; ++i) {
+            h ^= (v >> (8 * i)) & 0xff;
+            h *= 0x100000001b3ull;
+        }
+    };
+    mix(targets.size());
+    for (Origin *o : targets) mix((uint64_t)(uintptr_t)o);
+    mix(inputs.size());
+    for (Origin *o : inputs) mix((uint64_t)(uintptr_t)o);
+    return h;
+}
 
 bool Session::get(const Var &v, Tensor *out) const {
     auto it = data.find(v.key());
@@ -777,8 +798,14 @@ sage_status Session::eval(const std::vector<Var> &targets) {
     for (const Var &v : x) xk.push_back(v.key());
     std::sort(xk.begin(), xk.end());
     Program *prog = nullptr;
-    for (auto &c : cache_)
-        if (c->target_keys == tk && c->x_keys == xk && (!c->row || row_program_ready(*c->row, *this))) prog = c.get();
+    const uint64_t key_hash = program_key_hash(tk, xk);
+    for (size_t i = cache_.size(); i-- > 0;) {
+        Program *c = cache_[i].get();
+        if (c->key_hash != key_hash || c->target_keys != tk || c->x_keys != xk || (c->row && !row_program_ready(*c->row, *this))) continue;
+        prog = c;
+        if (i + 1 != cache_.size()) std::rotate(cache_.begin() + (long)i, cache_.begin() + (long)i + 1, cache_.end());  // now the most recent
+        break;
+    }
     if (!prog) {
         std::unique_ptr<Program> p;
         try {
@@ -806,7 +833,12 @@ sage_status Session::eval(const std::vector<Var> &targets) {
         }
         p->target_keys = tk;
         p->x_keys = xk;
+        p->key_hash = key_hash;
         prog = p.get();
+        if (cache_.size() >= kMaxPrograms) {
+            if (last_ == cache_.front().get()) last_ = nullptr;
+            cache_.erase(cache_.begin());  // the least recently used program and everything only it kept alive
+        }
         cache_.push_back(std::move(p));
         ++programs_compiled;
     }

@@ -440,3 +440,39 @@ def test_bert_training_plan():
     d = c.describe()
     assert "row_program[4096x768" in d and "row_program[49152x128" in d
     c.close()
+
+
+def test_program_cache_is_bounded_and_least_recently_used():
+    """A loop that builds a fresh graph per step (a new input Var per batch) must not grow the session: compiled
+    programs are kept up to a limit, least recently used dropped first, and a dropped program lets go of the
+    tensors only it kept alive."""
+    ctx = S.Context(-1)
+    try:
+        w = ctx.var(np.ones((64, 64), np.float32))
+        _, limit = ctx.programs_cached()
+        assert 8 <= limit <= 64
+        first = (ctx.var(np.zeros((256, 64), np.float32)).matmul(w) + 1.0)
+        ctx.eval(first)
+        used = []
+        for i in range(3 * limit):
+            x = ctx.var(np.zeros((256, 64), np.float32))      # a fresh leaf: a new program every time
+            y = S.relu(x.matmul(w) + 1.0)
+            ctx.eval(y)
+            ctx.clear()
+            del x, y
+            if i % 7 == 0:                                    # keep `first` recent: it must survive
+                before = ctx.programs_compiled()
+                ctx.eval(first)
+                ctx.clear()
+                assert ctx.programs_compiled() == before
+            used.append(ctx.mem_stats()["mem_used"])
+            assert ctx.programs_cached()[0] <= limit
+        assert ctx.programs_cached()[0] == limit
+        assert max(used[limit + 2:]) <= max(used[:limit + 2])  # memory in use stops growing once the cache is full
+        ctx.drop_programs()
+        assert ctx.programs_cached()[0] == 0
+        before = ctx.programs_compiled()
+        ctx.eval(first)
+        assert ctx.programs_compiled() == before + 1
+    finally:
+        ctx.close()
