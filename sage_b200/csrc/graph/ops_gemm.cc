@@ -11,7 +11,9 @@
 //   * the elementwise map that consumes the product (bias, residual, scale + mask, relu ...) becomes
 //     the GEMM's epilogue expression;
 //   * a permuted copy of the product (head merge) becomes the GEMM's store pattern;
-//   * the product's tf32 hi/lo planes are written by the epilogue when another GEMM reads it next.
+//   * the product's tf32 hi/lo planes are written by the epilogue when another GEMM reads it next;
+//   * gemm(softmax(gemm{f}(Q, K)), V) — the attention block of src/models/bert.rs:250-280 — becomes ONE operator
+//     that runs the fused attention kernel: scores and probabilities never exist in memory.
 #include <cuda_runtime.h>
 
 #include <cstdlib>
@@ -182,10 +184,15 @@ struct GemmOp : Operator {
     bool row_softmax = false;       // the stored value is softmax over the last axis of the (epilogue of the) product
     bool folded = false;            // result stored through (ldc, sc0, sc1, nbc0) instead of row-major [batch, M, N]
     long long ldc = 0, sc0 = 0, sc1 = 0, nbc0 = 1;
+    // Fused attention: the operator is softmax_rows(f(Q K^T)) V.  in = {Q, V, K, operands of f...}; m = queries,
+    // n = head columns, k = keys; ta / tb keep describing the outer product (P V), score_ta / score_tb the inner
+    // one (Q K); `epilogue`, `epi_ext` and `epi_group` are f and its index space (that of the score matrix).
+    bool attn = false, score_ta = false, score_tb = false;
 
-    const char *name() const override { return batched ? "gemm_batched" : "gemm"; }
+    const char *name() const override { return attn ? "attention" : batched ? "gemm_batched" : "gemm"; }
     Cat cat() const override { return Cat::Contract; }
-    int naux() const { return (int)in.size() - 2; }
+    int first_aux() const { return attn ? 3 : 2; }
+    int naux() const { return (int)in.size() - first_aux(); }
 
     std::vector<Var> grad(const std::vector<Var> &x, const Var &, const Var &gy) override {  // gemm.rs:150-163,304-328
         if (lowered) shape_fail("a lowered gemm is not differentiated");
@@ -216,6 +223,7 @@ struct GemmOp : Operator {
         sage_status st = Tensor::uninit(ctx, out, y);
         if (st) return st;
         if (!lowered) dims_from_inputs();
+        if (attn) return compute_attention(x, ctx, y, emit, only);
         if (!lowered && (ctx.opts().gemm_backend == 1 || !k::gemm_tc_shape_ok(m, n, k, batch))) {
             const int o = batched ? 1 : 0;
             const Shape &a = x[0].desc.shape, &b = x[1].desc.shape;
@@ -338,25 +346,8 @@ struct GemmOp : Operator {
             if (!folded) g.nbc0 = e_nb0, g.sc0 = m * n, g.sc1 = m * n * e_nb0;
         }
         for (int i = 0; i < g.naux; ++i) {
-            const Tensor &t = x[2 + i];
-            const Shape &sh = t.desc.shape;
-            if (sh.extents != epi_ext) return ctx.fail(SAGE_ERR_INVALID, "internal: gemm epilogue operand extents changed");
-            long long gs[4] = {0, 0, 0, 0};
-            bool seen[4] = {false, false, false, false};
-            for (int d = (int)epi_ext.size() - 1; d >= 0; --d) {  // innermost axis of each group gives its stride
-                if (epi_ext[d] == 1) continue;
-                const int grp = epi_group[d];
-                if (!seen[grp]) {
-                    seen[grp] = true;
-                    gs[grp] = sh.strides[d];
-                }
-            }
-            if (!epilogue_operand_ok(sh, epi_ext, epi_group)) return ctx.fail(SAGE_ERR_INVALID, "internal: gemm epilogue operand is not addressable");
-            g.aux[i].ptr = (const float *)t.ptr();
-            g.aux[i].s1 = gs[GBatchHi];
-            g.aux[i].s0 = gs[GBatchLo];
-            g.aux[i].sr = gs[GRow];
-            g.aux[i].sc = (int)gs[GCol];
+            st = aux_strides(ctx, x[2 + i], &g.aux[i]);
+            if (st) return st;
         }
         // An epilogue cannot be applied before the K slices of a split product are summed.  Where the cost model
         // wants slices (few output tiles, long K: a convolution of a small feature map at a small batch), the
@@ -396,6 +387,88 @@ struct GemmOp : Operator {
         return k::gemm_tc_run(ctx, g);
     }
     MapCache epi_cache;  // the epilogue as a map kernel, for products that are cut into K slices
+
+    // Strides of an epilogue operand per axis group (batch high, batch low, row, column) and the number of
+    // low-batch steps, from the operand's run-time shape.
+    sage_status aux_strides(Context &ctx, const Tensor &t, k::TcAuxArg *out) const {
+        const Shape &sh = t.desc.shape;
+        if (sh.extents != epi_ext) return ctx.fail(SAGE_ERR_INVALID, "internal: gemm epilogue operand extents changed");
+        long long gs[4] = {0, 0, 0, 0};
+        bool seen[4] = {false, false, false, false};
+        for (int d = (int)epi_ext.size() - 1; d >= 0; --d) {  // innermost axis of each group gives its stride
+            if (epi_ext[d] == 1) continue;
+            const int grp = epi_group[d];
+            if (!seen[grp]) {
+                seen[grp] = true;
+                gs[grp] = sh.strides[d];
+            }
+        }
+        if (!epilogue_operand_ok(sh, epi_ext, epi_group)) return ctx.fail(SAGE_ERR_INVALID, "internal: gemm epilogue operand is not addressable");
+        out->ptr = (const float *)t.ptr();
+        out->s1 = gs[GBatchHi];
+        out->s0 = gs[GBatchLo];
+        out->sr = gs[GRow];
+        out->sc = (int)gs[GCol];
+        return SAGE_OK;
+    }
+
+    sage_status compute_attention(const std::vector<Tensor> &x, Context &ctx, Tensor *y, bool emit, bool only) {
+        k::TcAttn a;
+        a.lq = m;
+        a.lk = k;
+        a.d = n;
+        a.batch = batch;
+        std::shared_ptr<SplitCache> hold_q, hold_k, hold_v;
+        bool sw_q = false, sw_k = false, sw_v = false;
+        sage_status st = make_operand(ctx, x[0], &a.q, &sw_q, &hold_q);
+        if (!st) st = make_operand(ctx, x[2], &a.k, &sw_k, &hold_k);
+        if (!st) st = make_operand(ctx, x[1], &a.v, &sw_v, &hold_v);
+        if (st) return st;
+        a.q_kmajor = (!score_ta) != sw_q;  // Q lies as [queries, head columns] unless transposed
+        a.k_kmajor = score_tb != sw_k;     // K as operand B of Q K: [head columns, keys] unless transposed
+        a.v_kmajor = tb != sw_v;           // V as operand B of P V: [keys, head columns] unless transposed
+        if (a.q.nb0 * a.q.nb1 != batch || a.k.nb0 * a.k.nb1 != batch || a.v.nb0 * a.v.nb1 != batch)
+            return ctx.fail(SAGE_ERR_INVALID, "attention: operand batch extents differ from the operator's");
+        a.o = (float *)y->ptr();
+        if (folded) {
+            a.ldo = ldc;
+            a.so0 = sc0;
+            a.so1 = sc1;
+            a.nbo0 = nbc0;
+        } else {
+            a.ldo = n;
+            a.so0 = m * n;
+            a.so1 = 0;
+            a.nbo0 = batch;
+        }
+        if (emit) {
+            st = storage_planes_attach(ctx, *y->data);
+            if (st) return st;
+            a.o_hi = y->data->split->planes.planes + y->desc.shape.offset;
+            a.o_plane = y->data->split->plane;
+            if (only) {
+                a.o = nullptr;
+                y->data->planes_only = true;
+            }
+        }
+        a.naux = naux();
+        a.epilogue = epilogue;
+        a.nbe0 = batch;
+        if (a.naux > 0) {
+            a.nbe0 = 1;
+            bool any_hi = false;
+            for (size_t d = 0; d < epi_ext.size(); ++d) {
+                if (epi_group[d] == GBatchLo) a.nbe0 *= epi_ext[d];
+                if (epi_group[d] == GBatchHi && epi_ext[d] > 1) any_hi = true;
+            }
+            if (!any_hi && a.nbe0 != batch) return ctx.fail(SAGE_ERR_INVALID, "internal: attention expression batch groups do not cover the batch");
+        }
+        for (int i = 0; i < a.naux; ++i) {
+            st = aux_strides(ctx, x[3 + i], &a.aux[i]);
+            if (st) return st;
+        }
+        return k::attention_tc_run(ctx, a);
+    }
 
     // Each group's axes must step through the operand like one axis (or not at all), and the
     // column group with stride 0 or 1.
@@ -546,7 +619,7 @@ std::shared_ptr<Operator> gemm_with_store(const Operator &op, const Shape &view,
     }
     if (seen[GCol] && gdst[GCol] != 1) return nullptr;
     if (gspan[GCol] != c->n || gspan[GRow] != c->m) return nullptr;
-    if (!c->epilogue.empty()) {  // the epilogue operands and the store must cut the batch the same way
+    if (!c->epilogue.empty() && !c->attn) {  // the epilogue operands and the store must cut the batch the same way
         long long e_nb0 = 1;
         for (size_t d = 0; d < c->epi_ext.size(); ++d)
             if (c->epi_group[d] == GBatchLo) e_nb0 *= c->epi_ext[d];
@@ -576,6 +649,37 @@ std::shared_ptr<Operator> gemm_with_row_softmax(const Operator &op, long long ro
     return c;
 }
 
+// gemm(softmax_rows(score), V) where score = gemm{f}(Q, K) on the tensor cores: one fused attention operator.
+// `rows` x `cols` is the softmax's row space.  Null when the shapes do not fit the kernel (head columns <= 64,
+// softmax over exactly the keys) or an operand is something TMA cannot read.
+std::shared_ptr<Operator> gemm_with_attention(const Operator &outer_op, const Operator &score_op, long long rows, long long cols, bool tc_enabled) {
+    const GemmOp *o = as_gemm(outer_op), *s = as_gemm(score_op);
+    if (!o || !s || !tc_enabled || o->attn || s->attn || o->conv || s->conv || o->folded || s->folded || o->row_softmax || s->row_softmax) return nullptr;
+    if (!o->epilogue.empty() || o->naux() != 0 || o->ta || s->naux() > 3) return nullptr;
+    if (!gemm_runs_on_tc(outer_op, tc_enabled) || !gemm_runs_on_tc(score_op, tc_enabled)) return nullptr;
+    auto c = lowered_clone(*o);
+    auto sc = lowered_clone(*s);
+    if (c->batch != sc->batch || c->m != sc->m || c->k != sc->n || cols != sc->n || rows != sc->batch * sc->m) return nullptr;
+    if (!k::attention_tc_shape_ok(c->m, c->k, c->n, c->batch) || sc->k != c->n) return nullptr;  // queries and values share the head width here
+    for (const TensorDesc &d : {sc->in[0], sc->in[1], c->in[1]})
+        if (d.dtype != SAGE_F32 || !gemm_operand_view_ok(d.shape)) return nullptr;
+    c->attn = true;
+    c->score_ta = sc->ta;
+    c->score_tb = sc->tb;
+    c->epilogue = sc->epilogue;
+    c->epi_ext = sc->epi_ext;
+    c->epi_group = sc->epi_group;
+    const TensorDesc v = c->in[1];
+    c->in = {sc->in[0], v, sc->in[1]};
+    for (int i = 0; i < sc->naux(); ++i) c->in.push_back(sc->in[2 + i]);
+    return c;
+}
+
+bool is_attention_op(const Operator &op) {
+    const GemmOp *g = as_gemm(op);
+    return g && g->attn;
+}
+
 bool is_gemm_op(const Operator &op) { return as_gemm(op) != nullptr; }
 
 // gemm(reshape(im2col(x)), W): the column matrix is never stored as fp32 — the GEMM makes its tf32
@@ -601,13 +705,14 @@ bool gemm_operand_static_direct(const Operator &op, int idx) {
     if (is_grouped_gemm_op(op)) return idx == 0 && gemm_operand_view_ok(op.in[0].shape);
     const GemmOp *g = as_gemm(op);
     if (g && g->conv && idx == 0) return g->conv_implicit();  // implicit GEMM reads the image's planes; else im2col reads fp32
-    return g && idx >= 0 && idx < 2 && gemm_operand_view_ok(g->in[idx].shape);
+    return g && idx >= 0 && idx < (g->attn ? 3 : 2) && gemm_operand_view_ok(g->in[idx].shape);
 }
 
 std::string describe_gemm(const Operator &op) {
     const GemmOp *g = as_gemm(op);
     if (!g) return "";
     std::string s;
+    if (g->attn) return "{" + (g->epilogue.empty() ? std::string("x0") : g->epilogue) + "}" + (g->folded ? "[store]" : "");
     if (g->conv) s += g->conv_implicit() ? "<implicit conv>" : "<im2col>";
     if (!g->epilogue.empty()) s += "{" + g->epilogue + "}";
     if (g->row_softmax) s += "|softmax";
@@ -762,7 +867,7 @@ bool is_grouped_gemm_op(const Operator &op) { return dynamic_cast<const GroupedG
 // (same A view, same shape and transposes, same epilogue text); the caller adds A's identity.
 bool gemm_group_key(const Operator &op, std::string *key) {
     const GemmOp *g = as_gemm(op);
-    if (!g || !g->lowered || g->folded || g->conv || g->row_softmax || g->batch != 1 || g->naux() > 1) return false;
+    if (!g || !g->lowered || g->attn || g->folded || g->conv || g->row_softmax || g->batch != 1 || g->naux() > 1) return false;
     if (g->n % 4 || g->k % 4 || !g->in[1].shape.has_default_strides() || g->in[1].shape.rank() != 2) return false;
     if (g->naux() == 1) {  // the one epilogue operand must be a row vector broadcast over the rows
         const Shape &b = g->in[2].shape;

@@ -49,6 +49,8 @@ std::shared_ptr<Operator> gemm_with_store(const Operator &op, const Shape &view,
 bool row_op_emits_planes(const Operator &op);
 bool row_op_is_softmax(const Operator &op, long long *rows, long long *cols);
 std::shared_ptr<Operator> gemm_with_row_softmax(const Operator &op, long long rows, long long cols, const TensorDesc &out, bool tc_enabled);
+std::shared_ptr<Operator> gemm_with_attention(const Operator &outer_op, const Operator &score_op, long long rows, long long cols, bool tc_enabled);
+bool is_attention_op(const Operator &op);
 bool is_grouped_gemm_op(const Operator &op);
 bool gemm_operand_static_direct(const Operator &op, int idx);
 bool gemm_group_key(const Operator &op, std::string *key);
@@ -191,6 +193,7 @@ static Node build(const Var &v, const std::unordered_set<Origin *> &inputs, bool
 //   gemm(.. reshape(copy(view)) ..)        the operand is read through `view`; the copy goes away
 //   map(.. reshape(gemm) .., aux ..)       the map's expression becomes the GEMM's epilogue
 //   copy(permute(reshape(gemm)))           the permutation becomes the GEMM's store pattern
+//   gemm(reshape(softmax(gemm{f}(q, k))), v)   one fused attention operator (scores and probabilities stay on chip)
 // Every fold is checked against the static strides and declined when TMA or the epilogue's
 // addressing cannot express it; what is declined simply stays a separate kernel.
 static bool reshape_keeps_matrix(const Operator &op) {
@@ -199,9 +202,15 @@ static bool reshape_keeps_matrix(const Operator &op) {
     return ra >= 2 && rb >= 2 && a[ra - 1] == b[rb - 1] && a[ra - 2] == b[rb - 2];
 }
 
-static void lower(Node &n, bool tc, bool softmax_in_gemm) {
+// The fused attention kernel is used unless pattern_fusion bit 3 (value 8) or SAGE_ATTENTION=0 says otherwise.
+static bool attention_enabled() {
+    static const bool on = !(getenv("SAGE_ATTENTION") && atoi(getenv("SAGE_ATTENTION")) == 0);
+    return on;
+}
+
+static void lower(Node &n, bool tc, bool softmax_in_gemm, bool attention) {
     if (n.is_data) return;
-    for (Node &a : n.args) lower(a, tc, softmax_in_gemm);
+    for (Node &a : n.args) lower(a, tc, softmax_in_gemm, attention);
     // operands behind an organize() copy
     if (is_gemm_op(*n.op) && gemm_runs_on_tc(*n.op, tc)) {
         {  // the column matrix of a convolution: made by the GEMM itself, as planes
@@ -225,6 +234,27 @@ static void lower(Node &n, bool tc, bool softmax_in_gemm) {
             Node inner = std::move(p->args[0]);
             n.args[idx] = std::move(inner);
             n.op = f;
+        }
+        if (attention && n.args.size() == 2) {  // the probabilities of an attention block times the values
+            Node *p = &n.args[0];
+            while (!p->is_data && is_reshape_op(*p->op)) p = &p->args[0];
+            long long rows = 0, cols = 0;
+            if (!p->is_data && row_op_is_softmax(*p->op, &rows, &cols) && p->args.size() == 1) {
+                Node *s = &p->args[0];
+                while (!s->is_data && is_reshape_op(*s->op)) s = &s->args[0];
+                if (!s->is_data && !s->shared && is_gemm_op(*s->op) && s->args.size() >= 2) {
+                    std::shared_ptr<Operator> f = gemm_with_attention(*n.op, *s->op, rows, cols, tc);
+                    if (f) {
+                        std::vector<Node> score_args = std::move(s->args);
+                        std::vector<Node> args;
+                        args.push_back(std::move(score_args[0]));  // Q
+                        args.push_back(std::move(n.args[1]));      // V
+                        for (size_t i = 1; i < score_args.size(); ++i) args.push_back(std::move(score_args[i]));  // K, operands of f
+                        n.op = f;
+                        n.args = std::move(args);
+                    }
+                }
+            }
         }
         return;
     }
@@ -360,7 +390,7 @@ static void mark_plane_readers(Node &n, bool tc, std::unordered_set<Origin *> *s
     for (Node &a : n.args) mark_plane_readers(a, tc, states);
     const bool grouped = is_grouped_gemm_op(*n.op);
     if (!grouped && (!is_gemm_op(*n.op) || !gemm_runs_on_tc(*n.op, tc))) return;
-    for (int idx = 0; idx < (grouped ? 1 : 2); ++idx) {
+    for (int idx = 0; idx < (grouped ? 1 : is_attention_op(*n.op) ? 3 : 2); ++idx) {
         Node *p = skip_views(&n.args[idx]);
         if (p->is_data) {
             if (p->var.is_op() && gemm_operand_static_direct(*n.op, idx)) states->insert(p->var.key());
@@ -465,7 +495,7 @@ static std::vector<RowGroupPlan> plan_row_groups(const std::vector<Var> &order, 
 
 // Program::compile, session.rs:62-206.
 static std::unique_ptr<Program> compile(const std::vector<Var> &x, std::vector<Var> y, bool fusion, bool pattern, bool tc, bool softmax_in_gemm,
-                                        bool row_groups = false) {
+                                        bool row_groups = false, bool attention = false) {
     std::unique_ptr<Program> p(new Program());
     p->fusion = fusion;
     p->pattern = pattern;
@@ -581,7 +611,7 @@ static std::unique_ptr<Program> compile(const std::vector<Var> &x, std::vector<V
         }
         r.root = build(node, in_keys, fusion, pattern, true);
         if (pattern) {
-            lower(r.root, tc, softmax_in_gemm);
+            lower(r.root, tc, softmax_in_gemm, attention && tc && attention_enabled());
             if (tc) group_gemms(r.root);
         }
         p->routines.emplace(node.key(), std::move(r));
@@ -827,7 +857,7 @@ sage_status Session::eval(const std::vector<Var> &targets) {
             }
             if (!p)
                 p = compile(x, y, true, ctx_->opts().pattern_fusion != 0, ctx_->opts().gemm_backend != 1, (ctx_->opts().pattern_fusion & 2) != 0,
-                            (ctx_->opts().pattern_fusion & 5) == 1 && row_programs_enabled());
+                            (ctx_->opts().pattern_fusion & 5) == 1 && row_programs_enabled(), (ctx_->opts().pattern_fusion & 8) == 0);
         } catch (const ShapeError &e) {
             return ctx_->fail(SAGE_ERR_INVALID, e.msg);
         }

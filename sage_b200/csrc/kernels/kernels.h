@@ -136,6 +136,25 @@ struct TcGemm {
     int force_bn = 0;          // tile width chosen by the caller (64 / 128 / 192 / 256); 0 = the launcher's own choice
     bool no_split_k = false;   // never cut K into slices: the launch then needs no scratch from the allocator
 };
+// Fused attention: O[batch] = softmax_rows(f(Q[batch] K[batch]^T)) V[batch] in one launch (kernels/attn_tc_device.inc).
+// Q is lq x d, K is lk x d, V is lk x d per batch, each given as the tensor core reads it: `q` and `k` with rows =
+// tokens, cols = head columns when `*_kmajor` (the head columns are contiguous), else stored transposed (rows = head
+// columns, cols = tokens); `v` with rows = keys, cols = head columns when NOT `v_kmajor`, else stored transposed.
+// `epilogue` is f over x0 (the score) and x1.. (aux, addressed like a GEMM epilogue operand of the lq x lk score
+// matrix, batch cut by `nbe0`).  The result goes to o / o_hi exactly like TcGemm's c / c_hi.  d <= 64.
+struct TcAttn {
+    long long lq = 0, lk = 0, d = 0, batch = 1;
+    TcOperand q, k, v;
+    bool q_kmajor = true, k_kmajor = true, v_kmajor = false;
+    float *o = nullptr, *o_hi = nullptr;
+    long long o_plane = 0, ldo = 0, so0 = 0, so1 = 0, nbo0 = 1;
+    int naux = 0;
+    TcAuxArg aux[3];
+    long long nbe0 = 1;
+    std::string epilogue;  // empty = x0
+};
+bool attention_tc_shape_ok(long long lq, long long lk, long long d, long long batch);
+sage_status attention_tc_run(Context &ctx, const TcAttn &a);
 bool gemm_tc_shape_ok(long long m, long long n, long long k, long long batch);
 sage_status gemm_tc_run(Context &ctx, const TcGemm &g);
 // How many K slices gemm_tc_run would cut this product into (0 = none).  Only products without an epilogue are

@@ -413,3 +413,92 @@ def test_row_groups_do_not_swallow_a_state_that_lies_between_them():
     G = A @ w.astype(np.float64)
     B = ((A + G) * A).sum(1) + A.sum(1)
     assert gemm_err(outs[0][0], B.astype(np.float32)) <= 1e-4 and gemm_err(outs[0][1], G.astype(np.float32)) <= 1e-4
+
+
+# ------------------------------------------------------------------------------ fused attention
+def attention_graph(M, q, k, v, mask, n, heads, l, d):
+    """The attention block of src/models/bert.rs:250-280 with the public ops: separate heads, scores / sqrt(d) +
+    extended mask, softmax over the keys, probabilities x values, merge heads."""
+    def split(t):
+        return M.transpose(M.view(t, [n, l, heads, d]), 2, 1)
+    scores = M.matmul_batched(split(q), M.transpose(split(k), -1, -2)) / float(np.sqrt(np.float32(d)))
+    ext = (-(M.view(mask, [n, 1, 1, l])) + 1.0) * -1e5
+    p = M.softmax(scores + ext, [3])
+    av = M.transpose(M.matmul_batched(p, split(v)), 2, 1)
+    return M.view(av, [n, l, heads * d])
+
+
+@pytest.mark.parametrize("n,heads,l,d", [(2, 2, 128, 64), (3, 4, 512, 64), (2, 2, 70, 32), (2, 3, 200, 64), (1, 1, 64, 64), (2, 2, 129, 48),
+                                         (32, 12, 128, 64)])
+def test_fused_attention_vs_oracle_and_decomposed(n, heads, l, d):
+    """scores -> scale + mask -> softmax -> probabilities x values as ONE kernel (tcgen05, P kept in tensor memory)
+    against the oracle evaluating the reference's four-step composition, against the same graph evaluated kernel by
+    kernel (pattern_fusion bit 3 keeps the attention decomposed) and against float64.  Ragged padding masks; key
+    counts that are not multiples of the 64-key block (70, 129, 200); head widths 32 / 48 / 64; more than one key
+    block, where the running maximum rescales the partial sums: |a - b| / max(|b|, rms(b)) <= 1e-4 in every case."""
+    rng = np.random.default_rng(7000 + l + d)
+    e = heads * d
+    q, k, v = (rng.standard_normal((n, l, e)).astype(np.float32) * np.float32(s) for s in (1.5, 1.5, 1.0))
+    mask = np.ones((n, l), np.float32)
+    for i in range(n):
+        mask[i, l - int(rng.integers(0, l // 4 + 1)):] = 0
+    outs = []
+    for fusion in (1, 9):
+        c = S.Context(0, pattern_fusion=fusion)
+        try:
+            # the operands are results of kernels, as in the model: their producers write the tf32 planes
+            qv, kv, vv = (c.var(t) * 1.0 for t in (q, k, v))
+            y = attention_graph(S, qv, kv, vv, c.var(mask), n, heads, l, d)
+            c.trace_begin()
+            got = y.eval(c)
+            tr, desc = c.trace(), c.describe()
+            if fusion == 1:
+                assert "attention{" in desc and "attention_tc_3xtf32" in tr and "softmax_rows" not in tr, desc
+                assert sum(1 for t in tr if t.startswith("gemm")) == 0
+            else:
+                assert "attention" not in desc and "softmax_rows" in tr
+            assert c.status_word() == 0
+            outs.append(got)
+        finally:
+            c.close()
+    fused, plain = outs
+    q64, k64, v64 = (t.astype(np.float64).reshape(n, l, heads, d).transpose(0, 2, 1, 3) for t in (q, k, v))
+    s64 = q64 @ k64.transpose(0, 1, 3, 2) / np.float64(np.sqrt(np.float32(d))) + ((1.0 - mask.astype(np.float64)) * -1e5)[:, None, None, :]
+    ref64 = (softmax64(s64) @ v64).transpose(0, 2, 1, 3).reshape(n, l, e)
+    assert fused.shape == ref64.shape
+    assert gemm_err(fused, ref64) <= 1e-4 and gemm_err(plain, ref64) <= 1e-4
+    assert gemm_err(fused, plain) <= 1e-4
+    if n * heads * l * l <= 3 * 4 * 512 * 512:  # the oracle's scalar loops
+        from oracle import sage_ref as R
+        RV = lambda a: R.Var.new(R.Tensor.new(a))
+        ref = attention_graph(R, RV(q) * 1.0, RV(k) * 1.0, RV(v) * 1.0, RV(mask), n, heads, l, d).eval().numpy()
+        assert gemm_err(fused, ref) <= 1e-4
+
+
+def test_fused_attention_without_ref_compat_and_with_large_scores():
+    """With true identities (ref_compat = 0) the row maximum starts at -inf instead of 0, and scores far from 0 make the
+    running maximum move between key blocks: the rescaling path."""
+    rng = np.random.default_rng(7100)
+    n, heads, l, d = 2, 2, 256, 64
+    e = heads * d
+    q, k, v = (rng.standard_normal((n, l, e)).astype(np.float32) * np.float32(s) for s in (3.0, 3.0, 1.0))
+    q += np.float32(0.5)  # rows whose scores are all far below zero exist as well
+    mask = np.ones((n, l), np.float32)
+    mask[1, 200:] = 0
+    q64, k64, v64 = (t.astype(np.float64).reshape(n, l, heads, d).transpose(0, 2, 1, 3) for t in (q, k, v))
+    s64 = q64 @ k64.transpose(0, 1, 3, 2) / 8.0 + ((1.0 - mask.astype(np.float64)) * -1e5)[:, None, None, :]
+    ref64 = (softmax64(s64) @ v64).transpose(0, 2, 1, 3).reshape(n, l, e)
+    for compat in (0, 1):
+        c = S.Context(0, ref_compat=compat)
+        try:
+            y = attention_graph(S, c.var(q) * 1.0, c.var(k) * 1.0, c.var(v) * 1.0, c.var(mask), n, heads, l, d)
+            got = y.eval(c)
+            assert "attention{" in c.describe()
+            if compat == 0:
+                assert gemm_err(got, ref64) <= 1e-4
+            else:
+                # rows whose scores are all negative keep exp(x - 0): smaller terms, same quotient up to rounding
+                assert gemm_err(got, ref64) <= 1e-3
+            assert c.status_word() == 0
+        finally:
+            c.close()

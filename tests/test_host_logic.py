@@ -251,17 +251,18 @@ def test_bert_base_plan():
     c.trace_begin()
     c.eval(logits)
     t = c.trace()
-    assert t.count("layernorm_rows") == 25 and t.count("softmax_rows") == 12
+    # scores, scale + mask, softmax and probabilities x values of a layer are one fused attention launch
+    assert t.count("layernorm_rows") == 25 and t.count("softmax_rows") == 0 and t.count("attention_tc_3xtf32") == 12
     gemms = [k for k in t if k.startswith("gemm")]
-    assert len(gemms) == 12 * 6 + 1  # per layer: grouped Q/K/V, scores, P.V, output, FFN up, FFN down; + classifier
+    assert len(gemms) == 12 * 4 + 1  # per layer: grouped Q/K/V, output, FFN up, FFN down; + classifier
     k0, _ = c.launch_count()
     c.clear()
     c.eval(logits)
     # same program replayed; the tf32 splits of the 72 weight matrices are cached on their storages
     assert c.programs_compiled() == 1 and c.launch_count()[0] - k0 == len(t) - 72
     # Only the weights go through a split pass: every activation a GEMM reads gets its tf32 planes
-    # from the kernel that produces it (GEMM epilogue, softmax, layer norm).
-    assert t.count("split_tf32") == 72 and t.count("gemm_tc_3xtf32") == 72
+    # from the kernel that produces it (GEMM epilogue, attention, layer norm).
+    assert t.count("split_tf32") == 72 and t.count("gemm_tc_3xtf32") == 48
     # bias / residual / relu / scale+mask maps and the head split / merge copies are folded into the
     # GEMMs; what is left is the embedding sum, the per-layer mask bias and the classifier's two maps
     assert t.count("sage_map") == 1 + 12 + 2
@@ -269,11 +270,22 @@ def test_bert_base_plan():
     # the three projections of a layer input are one grouped launch, read back as three slabs;
     # "=planes": the only reader is a GEMM, so the fp32 result is not stored at all
     assert d.count("slab(gemm_grouped=planes(") == 36
-    assert d.count("gemm_batched[store]=planes") == 12                       # head merge = store pattern of P.V
-    assert d.count("gemm_batched{((x0 / sg_lit(0x41000000u)) + x1)}") == 12  # scores: scale + mask in the epilogue
+    # scale + mask is the expression between the score product and the softmax; head merge = the store pattern
+    assert d.count("attention{((x0 / sg_lit(0x41000000u)) + x1)}[store]=planes") == 12
     assert d.count("gemm{(((float)((x0 + x1) > sg_lit(0x00000000u))) * (x0 + x1))}=planes") == 12  # FFN up: bias + relu
     assert d.count("gemm{((x0 + x1) + x2)}") == 24                           # output / FFN down: bias + residual
-    assert d.count("softmax=planes") == 12 and d.count("layer_norm+planes") == 24  # layer norm also feeds the residual
+    assert d.count("softmax") == 0 and d.count("layer_norm+planes") == 24  # layer norm also feeds the residual
+    # pattern_fusion bit 3 keeps the attention block as separate kernels: two batched products around a row softmax
+    c9 = S.Context(-1, pattern_fusion=9)
+    m9 = S.Bert(num_layers=1)
+    for p in m9.params():
+        c9.set(p, np.zeros(p.extents, np.float32))
+    c9.trace_begin()
+    c9.eval(m9.pass_(c9.var(np.zeros((32, 128), np.uint32)), c9.var(np.ones((32, 128), np.float32))))
+    t9, d9 = c9.trace(), c9.describe()
+    assert t9.count("softmax_rows") == 1 and "attention_tc_3xtf32" not in t9 and t9.count("gemm_tc_3xtf32") == 6
+    assert "gemm_batched[store]=planes" in d9 and "gemm_batched{((x0 / sg_lit(0x41000000u)) + x1)}" in d9 and "softmax=planes" in d9
+    c9.close()
     # pattern_fusion bit 1: the softmax moves into the scores GEMM's epilogue (L = 128 keys fit one tile)
     c3 = S.Context(-1, pattern_fusion=3)
     m3 = S.Bert(num_layers=1)
