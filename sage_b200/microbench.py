@@ -8,6 +8,7 @@ row kernels and f32-equivalent TFLOP/s of the tensor-core GEMM, each as one JSON
   python -m sage_b200.microbench --case all
   python -m sage_b200.microbench --case train_resnet --batch 128             # examples/train.rs: one Adam step of ResNet-18
   python -m sage_b200.microbench --case train_bert                           # one Adam step of Bert base, batch 32 x 128 tokens
+  python -m sage_b200.microbench --case attention --batch 32 --heads 12 --seq 128 --d 64   # fused attention block
   python -m sage_b200.microbench --case tf32_peak                          # library TF32 GEMM: the tensor-pipe denominator
 
 Times are device times from CUDA events recorded on the context's stream in front of every launch
@@ -205,6 +206,48 @@ def case_train_bert(ctx, a):
             "mem_peak_gb": ctx.mem_stats()["mem_peak"] / 1e9}
 
 
+def case_attention(ctx, a):
+    """softmax(Q K^T / sqrt(d) + mask) V for [batch, heads, seq, d] as the model builds it (src/models/bert.rs:250-280):
+    one fused launch.  FLOPs: 2 * 2 * seq^2 * d per (batch, head); three times that on the tensor pipe (3xTF32)."""
+    n, h, l, d = a.batch, a.heads, a.seq, a.d
+    rng = np.random.default_rng(0)
+    q, k, v = (ctx.var(rng.standard_normal((n, l, h * d)).astype(np.float32)) for _ in range(3))
+    mask = ctx.var(np.ones((n, l), np.float32))
+
+    def split(t):
+        return S.transpose(S.view(t, [n, l, h, d]), 2, 1)
+    # the operands are results of kernels, as in the model, so that their producers write the tf32 planes
+    qv, kv, vv = q * 1.0, k * 1.0, v * 1.0
+    ctx.eval(qv, kv, vv)
+    scores = S.matmul_batched(split(qv), S.transpose(split(kv), -1, -2)) / float(np.sqrt(np.float32(d)))
+    p = S.softmax(scores + (-(S.view(mask, [n, 1, 1, l])) + 1.0) * -1e5, [3])
+    y = S.view(S.transpose(S.matmul_batched(p, split(vv)), 2, 1), [n, l, h * d])
+
+    ms, prof = timed_graph(ctx, y, [qv, kv, vv], a.reps, ["attention", "gemm", "softmax"])
+    flops = 4.0 * n * h * l * l * d
+    _, bf16, src = peaks()
+    return {"case": "attention", "batch": n, "heads": h, "seq": l, "d": d, "us": 1e3 * ms, "tflops_f32_equivalent": flops / (ms * 1e-3) / 1e12,
+            "tensor_pipe_tflops": 3 * flops / (ms * 1e-3) / 1e12, "frac_of_bf16_burst_half": 3 * flops / (ms * 1e-3) / 1e12 / (bf16 / 2),
+            "peak_source": src, "kernels": {k_: [c, t / a.reps * 1e3] for k_, (c, t) in prof.items()}}
+
+
+def timed_graph(ctx, y, keep, reps, names):
+    """Evaluates `y` `reps` times with `keep` held evaluated; device time of the kernels whose names start with `names`."""
+    def once():
+        ctx.clear()
+        ctx.eval(*keep)
+        ctx.eval(y)
+    for _ in range(3):
+        once()
+    ctx.sync()
+    ctx.profile_begin()
+    for _ in range(reps):
+        once()
+    prof = ctx.profile_end()
+    ms = sum(t for k, (n, t) in prof.items() if any(k.startswith(p) for p in names))
+    return ms / reps, prof
+
+
 def case_tf32_peak(a):
     """The tensor-pipe denominator for 3xTF32: the library TF32 GEMM (torch.matmul with TF32 allowed) at
     8192^3, measured like the bf16 figure of MEASURED_PEAKS.json — a burst of 10 and a loop of ~3 s."""
@@ -246,6 +289,9 @@ def main():
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=4096)
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--heads", type=int, default=12)
+    ap.add_argument("--seq", type=int, default=128)
+    ap.add_argument("--d", type=int, default=64)
     ap.add_argument("--top", type=int, default=10, help="training cases: how many kernels of the profiled step to list "
                     "(SAGE_VERBOSE_NAMES=1 gives one name per GEMM shape and map expression)")
     ap.add_argument("--device", type=int, default=0)
@@ -262,6 +308,8 @@ def main():
             r = case_config1(ctx, a)
         elif c == "train_resnet":
             r = case_train_resnet(ctx, a)
+        elif c == "attention":
+            r = case_attention(ctx, a)
         elif c == "train_bert":
             r = case_train_bert(ctx, a)
         else:

@@ -182,11 +182,12 @@ def test_transposed_and_strided_operand_views():
 
 def test_planes_only_intermediates():
     """When a product (or a softmax) is read by one GEMM and nothing else, only its tf32 planes are
-    written.  Evaluating just the block's output makes q/k/v, the probabilities, the merged context and
-    the FFN activation such intermediates; evaluating them as targets as well must give the same output."""
+    written.  Evaluating just the block's output makes q/k/v, the merged context and the FFN activation
+    such intermediates (and the probabilities, when the attention is kept decomposed: pattern_fusion bit 3);
+    evaluating them as targets as well must give the same output."""
     a = block_inputs(np.random.default_rng(321), 2, 128, 256, 512)
     ref = attention_block64(a, 4)
-    ctx, ctx2 = S.Context(0), S.Context(0)
+    ctx, ctx2, ctx3 = S.Context(0, pattern_fusion=9), S.Context(0, pattern_fusion=9), S.Context(0)
     try:
         t, _ = attention_block(ctx, a, 4)
         ctx.eval(t["out"])
@@ -199,9 +200,17 @@ def test_planes_only_intermediates():
         assert "softmax=planes" not in ctx2.describe()
         assert np.array_equal(got, ctx2.read(t2["out"]))  # the same kernels computed the same planes
         assert ctx.status_word() == 0
+        # with the fused attention kernel the probabilities do not exist at all; q / k / v and its output are planes only
+        t3, _ = attention_block(ctx3, a, 4)
+        ctx3.eval(t3["out"])
+        d3 = ctx3.describe()
+        assert "softmax" not in d3 and "[store]=planes" in d3 and d3.count("=planes") >= 4 and "attention{" in d3
+        assert gemm_err(ctx3.read(t3["out"]), ref["out"]) <= 1e-4 and gemm_err(ctx3.read(t3["out"]), got) <= 1e-5
+        assert ctx3.status_word() == 0
     finally:
         ctx.close()
         ctx2.close()
+        ctx3.close()
 
 
 def conv64(x, f, stride, pad, dil):
