@@ -305,6 +305,13 @@ void o_col2im(const float *col, float *img, int64_t batch, int64_t chan,
     }
 }
 
+/* The number of OpenMP threads the loops above use from now on.  A launcher may start the process with
+ * OMP_NUM_THREADS=1 (torch.distributed.run does); the timed CPU baseline sets what it wants explicitly. */
+void o_set_num_threads(int n) {
+    extern void omp_set_num_threads(int);
+    if (n > 0) omp_set_num_threads(n);
+}
+
 int o_num_threads(void) {
     int n = 1;
 #pragma omp parallel

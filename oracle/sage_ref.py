@@ -54,6 +54,12 @@ def num_threads():
     return int(_C.o_num_threads())
 
 
+def set_num_threads(n):
+    """OpenMP threads for the C loops (a launcher's OMP_NUM_THREADS=1 would otherwise make them serial)."""
+    _C.o_set_num_threads(int(n))
+    return num_threads()
+
+
 # --------------------------------------------------------------------------- shape
 class Shape:
     """src/shape.rs:37-279."""
