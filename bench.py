@@ -61,7 +61,7 @@ RESNET18_FLOPS_PER_IMAGE = 2 * 1814073344  # sage's d18 graph at 224 x 224 x 3, 
 # DRAM traffic of the dominant kernel (the tensor-core GEMM) per launch: dram__bytes_read.sum + dram__bytes_write.sum
 # summed by ncu over the GEMM launches of one step of this workload, divided by their number.  A profiler figure
 # cannot be taken inside a timed run; it is re-captured whenever the GEMM path changes.
-GEMM_DRAM_BYTES_PER_LAUNCH = 80.56e6
+GEMM_DRAM_BYTES_PER_LAUNCH = 89.59e6
 
 
 def tf32_library_peak(device):
@@ -395,14 +395,14 @@ def run_ours(args, rank, local_rank, world, dist):
     k0 = ctx.launch_count()[0]
     sampler = ClockSampler(local_rank)
     reps = []
-    for _ in range(REPEATS):
+    for _ in range(max(args.repeats, 1)):
         ctx.timer_start()
         for _ in range(args.steps):
             step_resident()
         reps.append(ctx.timer_stop())
         barrier()
     clocks = sampler.stop()
-    launches = (ctx.launch_count()[0] - k0) // REPEATS
+    launches = (ctx.launch_count()[0] - k0) // max(args.repeats, 1)
 
     # ---- roofline: the same K steps again with an event in front of every launch
     ctx.profile_begin()
@@ -445,9 +445,11 @@ def run_ours(args, rank, local_rank, world, dist):
     ctx.clear()
     ctx.drop_programs()
     del model, logits
-    extras = sharded_extras(S, ctx, dist, rank, world, local_rank, pk)
-    if world == 1:
-        extras.update(single_gpu_extras(S, ctx, pk))
+    extras = {}
+    if not args.no_extras:
+        extras = sharded_extras(S, ctx, dist, rank, world, local_rank, pk)
+        if world == 1:
+            extras.update(single_gpu_extras(S, ctx, pk))
     tf32_live = None
     if rank == 0:
         try:
@@ -465,6 +467,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="headline workload only (for short profiler captures)")
+    ap.add_argument("--repeats", type=int, default=REPEATS, help="repeats of the K-step timed region")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

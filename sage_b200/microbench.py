@@ -9,6 +9,7 @@ row kernels and f32-equivalent TFLOP/s of the tensor-core GEMM, each as one JSON
   python -m sage_b200.microbench --case train_resnet --batch 128             # examples/train.rs: one Adam step of ResNet-18
   python -m sage_b200.microbench --case train_bert                           # one Adam step of Bert base, batch 32 x 128 tokens
   python -m sage_b200.microbench --case attention --batch 32 --heads 12 --seq 128 --d 64   # fused attention block
+  python -m sage_b200.microbench --case conv --batch 32 --h 56 --c 64 --oc 64 --ker 3 --stride 1 --pad 1   # conv_2d, NHWC
   python -m sage_b200.microbench --case tf32_peak                          # library TF32 GEMM: the tensor-pipe denominator
 
 Times are device times from CUDA events recorded on the context's stream in front of every launch
@@ -206,6 +207,29 @@ def case_train_bert(ctx, a):
             "mem_peak_gb": ctx.mem_stats()["mem_peak"] / 1e9}
 
 
+def case_conv(ctx, a):
+    """conv_2d (src/ops/conv.rs:61-96) on [batch, h, h, c] with a [ker, ker, c, oc] filter through sage_conv2d_nhwc.
+    FLOPs: 2 * N * OH * OW * OC * KH * KW * C; three times that on the tensor pipe."""
+    n, h, c, oc, ker, stride, pad = a.batch, a.h, a.c, a.oc, a.ker, a.stride, a.pad
+    rng = np.random.default_rng(0)
+    oh = (h + 2 * pad - (ker - 1) - 1) // stride + 1
+    X = ctx.tensor(rng.standard_normal((n, h, h, c), dtype=np.float32))
+    F = ctx.tensor(rng.standard_normal((ker, ker, c, oc), dtype=np.float32) * np.float32(0.05))
+    Y = ctx.empty((n, oh, oh, oc))
+    cx, cf, cy, win = X.c(), F.c(), Y.c(), S.window(1, stride, pad, 1)
+
+    def go():
+        ctx._ck(S.lib.sage_conv2d_nhwc(ctx.h, ctypes.byref(cx), ctypes.byref(cf), ctypes.byref(win), ctypes.byref(cy)))
+    ms_all, prof = timed(ctx, go, a.reps, [""])
+    ms = sum(t for k_, (cnt, t) in prof.items() if k_.startswith("gemm")) / a.reps
+    flops = 2.0 * n * oh * oh * oc * ker * ker * c
+    _, bf16, src = peaks()
+    return {"case": "conv", "batch": n, "h": h, "c": c, "oc": oc, "ker": ker, "stride": stride, "pad": pad, "gemm_us": 1e3 * ms, "all_kernels_us": 1e3 * ms_all,
+            "tflops_f32_equivalent": flops / (ms * 1e-3) / 1e12, "tensor_pipe_tflops": 3 * flops / (ms * 1e-3) / 1e12,
+            "frac_of_bf16_burst_half": 3 * flops / (ms * 1e-3) / 1e12 / (bf16 / 2), "peak_source": src,
+            "kernels": {k_: [cnt, t / a.reps * 1e3] for k_, (cnt, t) in prof.items()}}
+
+
 def case_attention(ctx, a):
     """softmax(Q K^T / sqrt(d) + mask) V for [batch, heads, seq, d] as the model builds it (src/models/bert.rs:250-280):
     one fused launch.  FLOPs: 2 * 2 * seq^2 * d per (batch, head); three times that on the tensor pipe (3xTF32)."""
@@ -289,6 +313,12 @@ def main():
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=4096)
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--h", type=int, default=56)
+    ap.add_argument("--c", type=int, default=64)
+    ap.add_argument("--oc", type=int, default=64)
+    ap.add_argument("--ker", type=int, default=3)
+    ap.add_argument("--stride", type=int, default=1)
+    ap.add_argument("--pad", type=int, default=1)
     ap.add_argument("--heads", type=int, default=12)
     ap.add_argument("--seq", type=int, default=128)
     ap.add_argument("--d", type=int, default=64)
@@ -308,6 +338,8 @@ def main():
             r = case_config1(ctx, a)
         elif c == "train_resnet":
             r = case_train_resnet(ctx, a)
+        elif c == "conv":
+            r = case_conv(ctx, a)
         elif c == "attention":
             r = case_attention(ctx, a)
         elif c == "train_bert":
