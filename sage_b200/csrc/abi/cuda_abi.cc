@@ -11,7 +11,8 @@ using namespace sage;
 
 #define CTX_OR_FAIL(c)                    \
     if (!(c) || !(c)->impl) return SAGE_ERR_INVALID; \
-    Context &C = *(c)->impl
+    Context &C = *(c)->impl;                         \
+    C.make_current()
 
 static void *tensor_ptr(const sage_tensor *t) { return static_cast<char *>(t->buf->ptr) + t->offset * 4; }
 

@@ -82,6 +82,7 @@ static sage_status upload_into(Context &C, Tensor *t, const void *data, bool asy
 sage_status sage_var_from_host(sage_session *s, int32_t dtype, int32_t ndim, const int64_t *extents, const void *data, sage_var **out) {
     return guarded([&]() -> sage_status {
         Context &C = s->impl->ctx();
+        C.make_current();
         Tensor t;
         sage_status st = Tensor::uninit(C, TensorDesc(infer_extents(arr(ndim, extents), 0), dtype), &t);
         if (st) return st;
@@ -102,6 +103,7 @@ sage_status sage_var_empty(int32_t dtype, int32_t ndim, const int64_t *extents, 
 sage_status sage_var_set(sage_session *s, sage_var *v, const void *data, int32_t async) {
     return guarded([&]() -> sage_status {
         Context &C = s->impl->ctx();
+        C.make_current();
         if (v->v.is_op()) shape_fail("can only assign tensor to the data variable");
         Tensor &cur = v->v.origin->data;
         // Reuse the variable's buffer when it is exclusively owned, contiguous and of the right size.
@@ -141,6 +143,7 @@ sage_status sage_var_info(const sage_var *v, int32_t *dtype, int32_t *ndim, int6
 sage_status sage_eval(sage_session *s, sage_var *const *targets, int32_t n) {
     std::vector<Var> t;
     for (int i = 0; i < n; ++i) t.push_back(targets[i]->v);
+    s->impl->ctx().make_current();
     sage_status st = s->impl->eval(t);
     if (st) g_error = s->impl->ctx().last_error();
     return st;
@@ -148,6 +151,7 @@ sage_status sage_eval(sage_session *s, sage_var *const *targets, int32_t n) {
 
 static sage_status tensor_of(sage_session *s, const Var &v, Tensor *t) {
     Context &C = s->impl->ctx();
+    C.make_current();
     if (v.is_op()) {
         if (!s->impl->get(v, t)) return C.fail(SAGE_ERR_INVALID, "variable has not been evaluated");
         return SAGE_OK;
@@ -162,6 +166,7 @@ static sage_status tensor_of(sage_session *s, const Var &v, Tensor *t) {
 sage_status sage_var_read(sage_session *s, const sage_var *v, void *dst, size_t bytes) {
     return guarded([&]() -> sage_status {
         Context &C = s->impl->ctx();
+        C.make_current();
         Tensor t;
         sage_status st = tensor_of(s, v->v, &t);
         if (st) {

@@ -60,6 +60,7 @@ extern "C" sage_status sage_gemm_noalloc(sage_ctx *ctx, int32_t trans_a, int32_t
     if (!ctx || !ctx->impl || !a || !b || !c) return SAGE_ERR_INVALID;
     Context &C = *ctx->impl;
     if (C.dry()) return C.fail(SAGE_ERR_NO_DEVICE, "sage_gemm_noalloc needs a CUDA device");
+    C.make_current();
     k::GemmArgs g{trans_a != 0, trans_b != 0, m, n, k, (const float *)a->ptr + a_off, lda, 0, (const float *)b->ptr + b_off, ldb, 0,
                   (float *)c->ptr + c_off, ldc, 0, 1};
     if (!k::gemm_tc_supported(g))

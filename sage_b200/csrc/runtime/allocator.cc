@@ -19,7 +19,10 @@ Allocator::~Allocator() {
     };
     collect(small_free_);
     collect(large_free_);
-    // Blocks still in use at teardown belong to leaked tensors; their segments are released too.
+    // Only segments whose blocks are all free are returned here.  A segment with a block still in use belongs to a
+    // tensor handle that outlives the context (Storage keeps the allocator alive through a shared_ptr, so this
+    // destructor normally runs after the last such handle is gone); should one remain, its segment is deliberately
+    // left to the process exit rather than freed under a live pointer.
     for (Block *h : heads) {
         bool all_free = true;
         for (Block *b = h; b; b = b->next) all_free &= b->free_;

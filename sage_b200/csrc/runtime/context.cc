@@ -136,6 +136,12 @@ sage_status Context::create(int device, const sage_ctx_opts &opts, Context **out
     return SAGE_OK;
 }
 
+void Context::make_current() const {
+    if (dry()) return;
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != device_) cudaSetDevice(device_);
+}
+
 Context::~Context() {
     if (!dry()) {
         cudaSetDevice(device_);

@@ -105,6 +105,10 @@ public:
     ~Context();
 
     int device() const { return device_; }
+    // Makes this context's GPU the calling thread's current device (kernel launches, attribute calls and
+    // cudaMalloc act on the current device, whatever stream they are given).  Every C-ABI entry point calls it, so
+    // a process may hold contexts on several GPUs, or change its device between calls.
+    void make_current() const;
     bool dry() const { return device_ < 0; }
     cudaStream_t stream() const { return stream_; }
     const sage_ctx_opts &opts() const { return opts_; }
