@@ -148,6 +148,8 @@ Context::~Context() {
         cudaStreamSynchronize(stream_);
         for (auto &kv : modules_)
             if (kv.second->cu_module && driver().ModuleUnload) driver().ModuleUnload(kv.second->cu_module);
+        if (streamk_block) alloc_->free(streamk_block);
+        streamk_block = nullptr;
         alloc_.reset();
         if (status_word_dev) cudaFree(status_word_dev);
         cudaStreamDestroy(stream_);

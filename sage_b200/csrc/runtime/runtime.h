@@ -160,6 +160,11 @@ public:
 
     void *timer_events[2] = {nullptr, nullptr};  // cudaEvent_t pair of sage_timer_start/stop
     uint32_t *status_word_dev = nullptr;  // device word kernels OR error bits into
+    // Scratch of the stream-K GEMM (partial accumulators of tiles shared between CTAs + their hand-over flags), taken
+    // from the pool on first use and kept; `streamk_epoch` is the value the flags of the next launch are raised to.
+    Block *streamk_block = nullptr;
+    size_t streamk_bytes = 0;
+    uint32_t streamk_epoch = 0;
     // Set by the evaluator around one operator's compute(): a tensor-core GEMM will read the result,
     // so a producer that can should also write the tf32 hi/lo planes of what it computes.
     bool hint_emit_planes = false;

@@ -751,3 +751,38 @@ def test_program_cache_and_allocator_reuse(ctx):
     assert ctx.mem_stats()["num_device_allocs"] - allocs0 <= 2  # blocks are recycled, not re-allocated
     assert all(np.allclose(o, 1.0 / 256) for o in outs)
     assert ctx.status_word() == 0
+
+
+@pytest.mark.parametrize("m,n,k,batch", [(4096, 768, 768, 1), (4096, 3072, 768, 1), (4096, 768, 3072, 1), (128, 25600, 512, 1), (512, 640, 1024, 5),
+                                         (300, 1000, 2100, 1), (4096, 768, 200, 1)])
+def test_gemm_shapes_whose_tiles_are_shared_between_ctas(ctx, monkeypatch, m, n, k, batch):
+    """Shapes whose whole tiles would fill the 148 SMs badly (64 pair tiles on 74 SM pairs, 2.6 waves, 100 tiles on 148
+    CTAs ...): with SAGE_GEMM_STREAMK=1 the CTAs share the (tile, K-block) space evenly and a tile cut between two or
+    three CTAs is summed through scratch (stream-K; off by default because it measured slower).  Checked against
+    float64 and the oracle, with the bias + residual epilogue of the model on the first shapes, run twice (the
+    hand-over flags change value per launch) with equal bits."""
+    monkeypatch.setenv("SAGE_GEMM_STREAMK", "1")  # read at every launch
+    rng = np.random.default_rng(2100 + n)
+    a = rng.uniform(-1, 1, (batch, m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (batch, k, n)).astype(np.float32)
+    f64 = a.astype(np.float64) @ b.astype(np.float64)
+    va, vb = ctx.var(a), ctx.var(b)
+    outs = []
+    for _ in range(2):
+        ctx.clear()
+        y = S.matmul_batched(va, vb) if batch > 1 else S.matmul(va.view([m, k]), vb.view([k, n]))
+        outs.append(y.eval(ctx).reshape(batch, m, n))
+    assert np.array_equal(outs[0], outs[1])
+    assert gemm_err(outs[0], f64) <= 1e-4
+    assert np.linalg.norm(outs[0] - f64) / np.linalg.norm(f64) <= 2e-6
+    if batch == 1 and m * n * k <= 4096 * 768 * 3072:
+        ref = R.matmul(RV(a[0]), RV(b[0])).eval().numpy()
+        assert gemm_err(outs[0][0], ref) <= 1e-4
+    if batch == 1 and n <= 3072:  # x W + bias + residual, as the output projection and the feed-forward products run
+        bias = rng.standard_normal((n,)).astype(np.float32)
+        res = rng.standard_normal((m, n)).astype(np.float32)
+        got = (S.matmul(va.view([m, k]), vb.view([k, n])) + ctx.var(bias) + ctx.var(res)).eval(ctx)
+        assert "gemm{" in ctx.describe()
+        assert gemm_err(got, f64[0] + bias + res) <= 1e-4
+    assert ctx.status_word() == 0
+    ctx.clear()
