@@ -206,6 +206,22 @@ struct GemmOp : Operator {
     // Implicit GEMM needs 32-channel K-blocks; images below 128 KiB take the explicit path (im2col-mode
     // tensor maps over very small tensors are avoided).
     bool conv_implicit() const { return conv && img[3] % 32 == 0 && img[0] * img[1] * img[2] * img[3] * 4 >= 131072; }
+    // At most 4 input channels (the first convolution of an image model): the image is re-laid with 4-float pixels so
+    // that the taps of a filter row are contiguous, and runs as an implicit GEMM over overlapping 32-float windows
+    // (kernels/conv.cu: pack_small_c_*); needs undilated columns, a window at most 8 wide and enough output pixels.
+    bool conv_small_c() const {
+        return conv && img[3] >= 1 && img[3] <= 4 && win.dil_w == 1 && win.ker_w >= 1 && win.ker_w <= 8 && n % 4 == 0 && img[0] * img[4] * img[5] >= 512;
+    }
+    struct PackedFilter {  // the filter as the B operand of that GEMM, kept until the filter is rewritten
+        const Storage *key = nullptr;
+        uint64_t version = 0;
+        std::shared_ptr<Allocator> alloc;
+        Block *block = nullptr;
+        ~PackedFilter() {
+            if (alloc && block) alloc->free(block);
+        }
+    };
+    std::shared_ptr<PackedFilter> packed_filter;
 
     void dims_from_inputs() {  // m, n, k, batch from in[0] / in[1] (last two axes = matrix)
         const Shape &a = in[0].shape, &b = in[1].shape;
@@ -252,7 +268,8 @@ struct GemmOp : Operator {
         g.batch = batch;
         std::shared_ptr<SplitCache> hold_a, hold_b;
         bool sw_a = false, sw_b = false;
-        Block *col_block = nullptr;  // conv: the column matrix exists only as tf32 planes, only for this launch
+        Block *col_block = nullptr;  // conv: the column matrix (or the channel-padded image) exists only as tf32 planes, only for this launch
+        bool small_c = false;
         if (conv && (!x[0].desc.shape.has_default_strides() || ta)) return ctx.fail(SAGE_ERR_INVALID, "internal: conv gemm needs a contiguous image");
         if (conv_implicit() && x[0].desc.shape.offset % 4 == 0) {
             // implicit GEMM: im2col-mode TMA reads the image's tf32 planes, nothing is materialised
@@ -269,8 +286,39 @@ struct GemmOp : Operator {
             g.conv.out_h = img[4];
             g.conv.out_w = img[5];
             g.conv.win = win;
+        } else if (conv_small_c() && x[1].desc.shape.has_default_strides()) {
+            if (x[0].data->planes_only) return ctx.fail(SAGE_ERR_INVALID, "internal: a planes-only image reached the channel-padding path");
+            const long long N = img[0], H = img[1], W = img[2], C = img[3], OH = img[4], OW = img[5];
+            // a row holds the left padding, the image, and enough behind it for the last pixel's 32-float window
+            const long long wp = std::max(W + 2 * win.pad_w, (OW - 1) * win.stride_w + 8);
+            const long long hp = std::max(H + 2 * win.pad_h, (OH - 1) * win.stride_h + (long long)(win.ker_h - 1) * win.dil_h + 1);
+            const long long plane = N * hp * wp * 4;
+            col_block = ctx.allocator().alloc((size_t)plane * 2 * sizeof(float));
+            if (!col_block) return ctx.fail(SAGE_ERR_OOM, "out of memory for the channel-padded image planes");
+            float *hi = reinterpret_cast<float *>(col_block->ptr);
+            st = k::pack_small_c_image(ctx, (const float *)x[0].ptr(), N, H, W, C, hp, wp, win.pad_h, win.pad_w, hi, plane);
+            if (st) {
+                ctx.allocator().free(col_block);
+                return st;
+            }
+            g.conv.on = true;
+            g.conv.hi = hi;
+            g.conv.plane = plane;
+            g.conv.n = N;
+            g.conv.h = hp;
+            g.conv.w = OW;          // window positions along a row, 4 * stride_w floats apart
+            g.conv.c = 32;          // a window: the (up to) 8 taps x 4 channels of one filter row
+            g.conv.out_h = OH;
+            g.conv.out_w = OW;
+            g.conv.sw = 4 * win.stride_w;
+            g.conv.sh = 4 * wp;
+            g.conv.sn = 4 * hp * wp;
+            g.conv.win = k::Window{1, win.ker_h, 1, win.stride_h, 0, 0, 1, win.dil_h};
+            g.k = (long long)win.ker_h * 32;
+            small_c = true;
         } else if (conv) {
             if (x[0].data->planes_only) return ctx.fail(SAGE_ERR_INVALID, "internal: a planes-only image reached the explicit im2col path");
+            if (!k::gemm_tc_shape_ok(m, n, k, batch)) return ctx.fail(SAGE_ERR_UNSUPPORTED, "conv_2d: a strided filter with so short a window is not supported");
             const int pitch = (int)((k + 3) / 4 * 4);
             const long long plane = m * pitch;
             col_block = ctx.allocator().alloc((size_t)plane * 2 * sizeof(float));
@@ -297,8 +345,30 @@ struct GemmOp : Operator {
                 if (b) c.allocator().free(b);
             }
         } free_col{ctx, col_block};
-        st = make_operand(ctx, x[1], &g.b, &sw_b, &hold_b);
-        if (st) return st;
+        if (small_c) {
+            const Storage *key = x[1].data.get();
+            if (!packed_filter || packed_filter->key != key || packed_filter->version != key->version) {
+                auto pf = std::make_shared<PackedFilter>();
+                pf->alloc = ctx.allocator_ptr();
+                pf->key = key;
+                pf->version = key->version;
+                const long long fplane = (long long)win.ker_h * 32 * n;
+                pf->block = ctx.allocator().alloc((size_t)fplane * 2 * sizeof(float));
+                if (!pf->block) return ctx.fail(SAGE_ERR_OOM, "out of memory for the re-laid filter");
+                st = k::pack_small_c_filter(ctx, (const float *)x[1].ptr(), win.ker_h, win.ker_w, (int)img[3], (int)n, reinterpret_cast<float *>(pf->block->ptr), fplane);
+                if (st) return st;
+                packed_filter = pf;
+            }
+            g.b.hi = reinterpret_cast<const float *>(packed_filter->block->ptr);
+            g.b.plane = (long long)win.ker_h * 32 * n;
+            g.b.ld = n;
+            g.b.rows = (long long)win.ker_h * 32;
+            g.b.cols = n;
+            if (tb) return ctx.fail(SAGE_ERR_INVALID, "internal: a convolution's filter operand is not transposed");
+        } else {
+            st = make_operand(ctx, x[1], &g.b, &sw_b, &hold_b);
+            if (st) return st;
+        }
         // A lies as [M,K] (K contiguous) unless transposed; B as [K,N] (N contiguous) unless transposed.
         g.a_kmajor = (!ta) != sw_a;
         g.b_kmajor = tb != sw_b;
@@ -689,12 +759,16 @@ std::shared_ptr<Operator> gemm_with_im2col(const Operator &op, const Operator &i
     const GemmOp *g = as_gemm(op);
     k::Window w;
     long long d[6];
-    if (!g || g->ta || g->conv || !gemm_runs_on_tc(op, tc_enabled) || !im2col_params(im2col_op, &w, d)) return nullptr;
+    if (!g || g->ta || g->conv || !tc_enabled || !im2col_params(im2col_op, &w, d)) return nullptr;
     auto c = lowered_clone(*g);
     if (c->batch != 1 || c->m != d[0] * d[4] * d[5] || c->k != (long long)w.ker_h * w.ker_w * d[3]) return nullptr;
     c->conv = true;
     c->win = w;
     for (int i = 0; i < 6; ++i) c->img[i] = d[i];
+    // With at most 4 channels the contraction the tensor cores see is KH x 32 long, whatever KH * KW * C is (a 3 x 3
+    // window over one channel has K = 9, below what the tiled path takes)
+    const bool as_small_c = c->conv_small_c() && !g->tb && k::gemm_tc_shape_ok(c->m, c->n, (long long)w.ker_h * 32, 1);
+    if (!as_small_c && !k::gemm_tc_shape_ok(c->m, c->n, c->k, c->batch)) return nullptr;
     c->in[0] = im2col_op.in[0];
     return c;
 }
@@ -713,7 +787,7 @@ std::string describe_gemm(const Operator &op) {
     if (!g) return "";
     std::string s;
     if (g->attn) return "{" + (g->epilogue.empty() ? std::string("x0") : g->epilogue) + "}" + (g->folded ? "[store]" : "");
-    if (g->conv) s += g->conv_implicit() ? "<implicit conv>" : "<im2col>";
+    if (g->conv) s += g->conv_implicit() ? "<implicit conv>" : g->conv_small_c() ? "<implicit conv, channels padded to 4>" : "<im2col>";
     if (!g->epilogue.empty()) s += "{" + g->epilogue + "}";
     if (g->row_softmax) s += "|softmax";
     if (g->folded) s += "[store]";

@@ -211,20 +211,22 @@ static bool attention_enabled() {
 static void lower(Node &n, bool tc, bool softmax_in_gemm, bool attention) {
     if (n.is_data) return;
     for (Node &a : n.args) lower(a, tc, softmax_in_gemm, attention);
-    // operands behind an organize() copy
-    if (is_gemm_op(*n.op) && gemm_runs_on_tc(*n.op, tc)) {
-        {  // the column matrix of a convolution: made by the GEMM itself, as planes
-            Node *p = &n.args[0];
-            while (!p->is_data && is_reshape_op(*p->op)) p = &p->args[0];
-            if (!p->is_data && p != &n.args[0] && p->args.size() == 1) {
-                std::shared_ptr<Operator> f = gemm_with_im2col(*n.op, *p->op, tc);
-                if (f) {
-                    Node inner = std::move(p->args[0]);
-                    n.args[0] = std::move(inner);
-                    n.op = f;
-                }
+    if (is_gemm_op(*n.op) && tc && n.args.size() == 2) {
+        // the column matrix of a convolution: made by the GEMM itself, as planes (this may also bring a product onto the
+        // tensor cores whose K = KH * KW * C alone is too short for them: a few-channel first layer)
+        Node *p = &n.args[0];
+        while (!p->is_data && is_reshape_op(*p->op)) p = &p->args[0];
+        if (!p->is_data && p != &n.args[0] && p->args.size() == 1) {
+            std::shared_ptr<Operator> f = gemm_with_im2col(*n.op, *p->op, tc);
+            if (f) {
+                Node inner = std::move(p->args[0]);
+                n.args[0] = std::move(inner);
+                n.op = f;
             }
         }
+    }
+    // operands behind an organize() copy
+    if (is_gemm_op(*n.op) && gemm_runs_on_tc(*n.op, tc)) {
         for (int idx = 0; idx < 2; ++idx) {
             Node *p = &n.args[idx];
             while (!p->is_data && is_reshape_op(*p->op) && reshape_keeps_matrix(*p->op)) p = &p->args[0];

@@ -289,6 +289,67 @@ sage_status im2col_planes(Context &ctx, const float *img, long long n, long long
     return ctx.check_cuda(cudaGetLastError(), "im2col launch");
 }
 
+// ---- convolutions with at most 4 input channels (the first layer of an image model: C = 3 or 1).
+// A channel run of 12 bytes is below TMA's 16-byte granularity, so the image is first re-laid as tf32 planes of
+// [N, H + pad, W + pad, 4] — channels padded to 4, the spatial padding written as zeros.  In that layout the KW taps of one
+// filter row are KW * 4 CONTIGUOUS floats, so one output pixel's operand row for tap row ky is a 32-float (128-byte)
+// window starting 4 * stride_w floats after its left neighbour's: an "image" of 32-channel pixels that overlap.  The
+// implicit-GEMM kernel then runs a (1 x KH) convolution over it; the column matrix is never written.
+__global__ void __launch_bounds__(256) pack_small_c_kernel(const float *__restrict__ img, float4 *__restrict__ hi, float4 *__restrict__ lo, long long n,
+                                                           int h, int w, int c, int hp, int wp, int pad_h, int pad_w) {
+    const long long total = n * hp * (long long)wp;
+    for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (long long)gridDim.x * blockDim.x) {
+        const int x = (int)(g % wp) - pad_w;
+        const long long r = g / wp;
+        const int y = (int)(r % hp) - pad_h;
+        const long long b = r / hp;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (x >= 0 && x < w && y >= 0 && y < h) {
+            const float *s = img + ((b * h + y) * (long long)w + x) * c;
+            for (int i = 0; i < c; ++i) v[i] = s[i];
+        }
+        float4 a, d;
+        sage_tc::split_tf32_value(v[0], &a.x, &d.x);
+        sage_tc::split_tf32_value(v[1], &a.y, &d.y);
+        sage_tc::split_tf32_value(v[2], &a.z, &d.z);
+        sage_tc::split_tf32_value(v[3], &a.w, &d.w);
+        hi[g] = a;
+        lo[g] = d;
+    }
+}
+
+// The filter [KH, KW, C, OC] as the matching B operand [KH * 32, OC]: row ky * 32 + kx * 4 + c; rows of padded
+// channels and of the window's unused tail are zero, so whatever the overlapping operand rows hold there is ignored.
+__global__ void __launch_bounds__(256) pack_small_c_filter_kernel(const float *__restrict__ f, float *__restrict__ hi, float *__restrict__ lo,
+                                                                  int kh, int kw, int c, int oc) {
+    const long long total = (long long)kh * 32 * oc;
+    for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (long long)gridDim.x * blockDim.x) {
+        const int o = (int)(g % oc), row = (int)(g / oc), ky = row / 32, r = row % 32, kx = r / 4, cc = r % 4;
+        const float v = (kx < kw && cc < c) ? f[(((long long)ky * kw + kx) * c + cc) * oc + o] : 0.f;
+        sage_tc::split_tf32_value(v, &hi[g], &lo[g]);
+    }
+}
+
+sage_status pack_small_c_image(Context &ctx, const float *img, long long n, long long h, long long w, long long c, long long hp, long long wp,
+                               int pad_h, int pad_w, float *hi, long long plane) {
+    ctx.note_launch("pack_small_c");
+    if (ctx.dry()) return SAGE_OK;
+    if (c < 1 || c > 4 || plane % 4 || reinterpret_cast<uintptr_t>(hi) % 16 || h > 0x7fffffffLL || w > 0x7fffffffLL || hp > 0x7fffffffLL || wp > 0x7fffffffLL)
+        return ctx.fail(SAGE_ERR_INVALID, "pack_small_c: bad arguments");
+    const long long total = n * hp * wp;
+    pack_small_c_kernel<<<grid_for(ctx, total), 256, 0, ctx.stream()>>>(img, reinterpret_cast<float4 *>(hi), reinterpret_cast<float4 *>(hi + plane), n, (int)h, (int)w,
+                                                                        (int)c, (int)hp, (int)wp, pad_h, pad_w);
+    return ctx.check_cuda(cudaGetLastError(), "pack_small_c launch");
+}
+
+sage_status pack_small_c_filter(Context &ctx, const float *filt, int kh, int kw, int c, int oc, float *hi, long long plane) {
+    ctx.note_launch("pack_small_c_filter");
+    if (ctx.dry()) return SAGE_OK;
+    if (kw * 4 > 32 || c > 4) return ctx.fail(SAGE_ERR_INVALID, "pack_small_c_filter: window too wide");
+    pack_small_c_filter_kernel<<<grid_for(ctx, (long long)kh * 32 * oc), 256, 0, ctx.stream()>>>(filt, hi, hi + plane, kh, kw, c, oc);
+    return ctx.check_cuda(cudaGetLastError(), "pack_small_c_filter launch");
+}
+
 sage_status im2col(Context &ctx, const float *img, float *col, long long n, long long img_h, long long img_w,
                    long long chan, long long col_h, long long col_w, const Window &w) {
     return im2col_planes(ctx, img, n, img_h, img_w, chan, col_h, col_w, w, col, nullptr, 0, 0);

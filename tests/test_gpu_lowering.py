@@ -511,3 +511,55 @@ def test_fused_attention_without_ref_compat_and_with_large_scores():
             assert c.status_word() == 0
         finally:
             c.close()
+
+
+@pytest.mark.parametrize("shape,filt,stride,pad,dil", [
+    ((4, 64, 64, 3), (7, 7, 3, 64), (2, 2), (3, 3), (1, 1)),        # the first convolution of ResNet (112-wide rows at full size)
+    ((3, 40, 44, 1), (3, 3, 1, 32), (1, 1), (1, 1), (1, 1)),        # one channel (the training example's 28 x 28 x 1 images)
+    ((2, 45, 51, 3), (3, 5, 3, 40), (3, 2), (2, 0), (1, 2)),        # unequal window / stride / padding, dilated rows
+    ((5, 32, 32, 3), (3, 3, 3, 32), (1, 1), (1, 1), (1, 1)),        # MobileNet's first layer (K = 27)
+    ((2, 50, 50, 4), (2, 8, 4, 32), (2, 1), (0, 1), (1, 1)),        # four channels, the widest window (8 taps x 4 floats = one 128-byte row)
+    ((2, 40, 40, 3), (3, 3, 3, 32), (1, 1), (1, 1), (2, 1)),        # dilated COLUMNS: not this path, the column planes are built
+])
+def test_convolution_with_few_input_channels(shape, filt, stride, pad, dil):
+    """conv_2d with C <= 4 (src/ops/conv.rs:61-96 at the first layer of the reference's image models).  A 12-byte channel
+    run cannot be a TMA box, so the image is re-laid with 4-float pixels (zero-padded in space as well) and the GEMM
+    reads overlapping 32-float windows of it: no column matrix is written.  Against float64, against the same graph
+    evaluated operator by operator, and — for the small cases — against the oracle."""
+    rng = np.random.default_rng(sum(shape) + sum(filt))
+    x = rng.standard_normal(shape).astype(np.float32)
+    f = (rng.standard_normal(filt) / np.sqrt(filt[0] * filt[1] * filt[2])).astype(np.float32)
+    b = rng.standard_normal(filt[3]).astype(np.float32)
+    ref = np.maximum(conv64(x, f, stride, pad, dil) + b, 0)
+    lowered, plain = S.Context(0), S.Context(0, pattern_fusion=0)
+    try:
+        outs = []
+        for ctx in (lowered, plain):
+            ctx.trace_begin()
+            y = S.relu(S.conv_2d(ctx.var(x), ctx.var(f), list(stride), list(pad), list(dil)) + ctx.var(b))
+            outs.append(y.eval(ctx))
+            outs.append(y.eval(ctx) if ctx is plain else None)
+        padded = dil[0] == 1
+        if padded:
+            assert "channels padded to 4" in lowered.describe() and "im2col" not in lowered.trace() and "pack_small_c" in lowered.trace()
+        else:
+            assert "channels padded" not in lowered.describe()
+        assert outs[0].shape == ref.shape
+        assert gemm_err(outs[0], ref) <= 1e-4 and gemm_err(outs[2], ref) <= 1e-4
+        assert gemm_err(outs[0], outs[2]) <= 1e-5
+        # a second evaluation reuses the re-laid filter; rewriting the filter must invalidate it
+        fv = lowered.var(f)
+        y2 = S.conv_2d(lowered.var(x), fv, list(stride), list(pad), list(dil))
+        first = y2.eval(lowered)
+        lowered.set(fv, (f * np.float32(-2)).astype(np.float32))
+        lowered.clear()
+        second = y2.eval(lowered)
+        assert gemm_err(second, -2 * conv64(x, f, stride, pad, dil)) <= 1e-4 and gemm_err(first, conv64(x, f, stride, pad, dil)) <= 1e-4
+        from oracle import sage_ref as R
+        RV = lambda a: R.Var.new(R.Tensor.new(a))
+        oref = R.conv_2d(RV(x), RV(f), list(stride), list(pad), list(dil)).eval().numpy()
+        assert gemm_err(first, oref) <= 1e-4
+        assert lowered.status_word() == 0
+    finally:
+        lowered.close()
+        plain.close()
