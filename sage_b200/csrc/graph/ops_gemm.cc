@@ -170,6 +170,15 @@ static sage_status make_operand(Context &ctx, const Tensor &t, k::TcOperand *op,
 // Axis groups of the epilogue's index space.
 enum { GBatchHi = 0, GBatchLo = 1, GRow = 2, GCol = 3 };
 
+// SAGE_CONV_RAW=1 (read at every use; off by default): convolutions read the image as plain fp32 and split every tile
+// into its tf32 planes inside the SM (TcConv::raw) instead of reading whole-image planes.  It halves the bytes operand
+// A moves from L2 into shared memory, but measured on B200 the four split warps do not keep up with the MMAs:
+// 56 x 56 x 64 -> 64 at batch 256: 717 -> 1311 us; 28 x 28 x 128: 388 -> 656 us; the 3-channel first layer 1301 -> 2229 us.
+static bool conv_raw_enabled() {
+    const char *e = getenv("SAGE_CONV_RAW");
+    return e && atoi(e) != 0;
+}
+
 struct GemmOp : Operator {
     bool ta = false, tb = false, batched = false;
     // ---- set by the evaluator's lowering; the defaults describe the plain operator
@@ -205,6 +214,9 @@ struct GemmOp : Operator {
 
     // Implicit GEMM needs 32-channel K-blocks; images below 128 KiB take the explicit path (im2col-mode
     // tensor maps over very small tensors are avoided).
+    // Opt-in: narrow products (at most 128 output channels) read the image as plain fp32 and split it per tile in
+    // shared memory.  Wider ones always keep whole-image planes (their kernels have no registers to spare for four more warps).
+    bool conv_raw() const { return conv_raw_enabled() && n <= 128; }
     bool conv_implicit() const { return conv && img[3] % 32 == 0 && img[0] * img[1] * img[2] * img[3] * 4 >= 131072; }
     // At most 4 input channels (the first convolution of an image model): the image is re-laid with 4-float pixels so
     // that the taps of a filter row are contiguous, and runs as an implicit GEMM over overlapping 32-float windows
@@ -272,13 +284,20 @@ struct GemmOp : Operator {
         bool small_c = false;
         if (conv && (!x[0].desc.shape.has_default_strides() || ta)) return ctx.fail(SAGE_ERR_INVALID, "internal: conv gemm needs a contiguous image");
         if (conv_implicit() && x[0].desc.shape.offset % 4 == 0) {
-            // implicit GEMM: im2col-mode TMA reads the image's tf32 planes, nothing is materialised
-            st = storage_planes(ctx, *x[0].data);
-            if (st) return st;
-            hold_a = x[0].data->split;
+            // implicit GEMM: im2col-mode TMA reads the image's tf32 planes, nothing is materialised (with SAGE_CONV_RAW=1:
+            // the plain fp32 image, split per tile inside the SM)
             g.conv.on = true;
-            g.conv.hi = hold_a->planes.planes + x[0].desc.shape.offset;
-            g.conv.plane = hold_a->plane;
+            if (conv_raw() && !x[0].data->planes_only) {
+                g.conv.hi = (const float *)x[0].ptr();
+                g.conv.plane = 0;
+                g.conv.raw = true;
+            } else {
+                st = storage_planes(ctx, *x[0].data);
+                if (st) return st;
+                hold_a = x[0].data->split;
+                g.conv.hi = hold_a->planes.planes + x[0].desc.shape.offset;
+                g.conv.plane = hold_a->plane;
+            }
             g.conv.n = img[0];
             g.conv.h = img[1];
             g.conv.w = img[2];
@@ -292,9 +311,10 @@ struct GemmOp : Operator {
             // a row holds the left padding, the image, and enough behind it for the last pixel's 32-float window
             const long long wp = std::max(W + 2 * win.pad_w, (OW - 1) * win.stride_w + 8);
             const long long hp = std::max(H + 2 * win.pad_h, (OH - 1) * win.stride_h + (long long)(win.ker_h - 1) * win.dil_h + 1);
-            const long long plane = N * hp * wp * 4;
-            col_block = ctx.allocator().alloc((size_t)plane * 2 * sizeof(float));
-            if (!col_block) return ctx.fail(SAGE_ERR_OOM, "out of memory for the channel-padded image planes");
+            const bool raw = conv_raw();  // plain fp32, split per tile inside the SM
+            const long long plane = raw ? 0 : N * hp * wp * 4;
+            col_block = ctx.allocator().alloc((size_t)(N * hp * wp * 4) * (raw ? 1 : 2) * sizeof(float));
+            if (!col_block) return ctx.fail(SAGE_ERR_OOM, "out of memory for the channel-padded image");
             float *hi = reinterpret_cast<float *>(col_block->ptr);
             st = k::pack_small_c_image(ctx, (const float *)x[0].ptr(), N, H, W, C, hp, wp, win.pad_h, win.pad_w, hi, plane);
             if (st) {
@@ -304,6 +324,7 @@ struct GemmOp : Operator {
             g.conv.on = true;
             g.conv.hi = hi;
             g.conv.plane = plane;
+            g.conv.raw = raw;
             g.conv.n = N;
             g.conv.h = hp;
             g.conv.w = OW;          // window positions along a row, 4 * stride_w floats apart
@@ -778,7 +799,7 @@ bool is_grouped_gemm_op(const Operator &op);
 bool gemm_operand_static_direct(const Operator &op, int idx) {
     if (is_grouped_gemm_op(op)) return idx == 0 && gemm_operand_view_ok(op.in[0].shape);
     const GemmOp *g = as_gemm(op);
-    if (g && g->conv && idx == 0) return g->conv_implicit();  // implicit GEMM reads the image's planes; else im2col reads fp32
+    if (g && g->conv && idx == 0) return g->conv_implicit() && !g->conv_raw();  // planes only when the kernel does not split the image itself
     return g && idx >= 0 && idx < (g->attn ? 3 : 2) && gemm_operand_view_ok(g->in[idx].shape);
 }
 

@@ -308,6 +308,10 @@ __global__ void __launch_bounds__(256) pack_small_c_kernel(const float *__restri
             const float *s = img + ((b * h + y) * (long long)w + x) * c;
             for (int i = 0; i < c; ++i) v[i] = s[i];
         }
+        if (!lo) {  // plain fp32: the GEMM splits each tile itself
+            hi[g] = make_float4(v[0], v[1], v[2], v[3]);
+            continue;
+        }
         float4 a, d;
         sage_tc::split_tf32_value(v[0], &a.x, &d.x);
         sage_tc::split_tf32_value(v[1], &a.y, &d.y);
@@ -337,7 +341,7 @@ sage_status pack_small_c_image(Context &ctx, const float *img, long long n, long
     if (c < 1 || c > 4 || plane % 4 || reinterpret_cast<uintptr_t>(hi) % 16 || h > 0x7fffffffLL || w > 0x7fffffffLL || hp > 0x7fffffffLL || wp > 0x7fffffffLL)
         return ctx.fail(SAGE_ERR_INVALID, "pack_small_c: bad arguments");
     const long long total = n * hp * wp;
-    pack_small_c_kernel<<<grid_for(ctx, total), 256, 0, ctx.stream()>>>(img, reinterpret_cast<float4 *>(hi), reinterpret_cast<float4 *>(hi + plane), n, (int)h, (int)w,
+    pack_small_c_kernel<<<grid_for(ctx, total), 256, 0, ctx.stream()>>>(img, reinterpret_cast<float4 *>(hi), plane ? reinterpret_cast<float4 *>(hi + plane) : nullptr, n, (int)h, (int)w,
                                                                         (int)c, (int)hp, (int)wp, pad_h, pad_w);
     return ctx.check_cuda(cudaGetLastError(), "pack_small_c launch");
 }

@@ -59,6 +59,7 @@ sage_status col2im(Context &ctx, const float *col, float *img, long long n, long
                    long long chan, long long col_h, long long col_w, const Window &w);
 // Convolutions with C <= 4: the image as tf32 planes [n, hp, wp, 4] (channels padded to 4, `pad_h` / `pad_w` zero rows /
 // columns in front, the rest behind), and the filter [kh, kw, c, oc] as planes [kh * 32, oc] with row ky * 32 + kx * 4 + c.
+// plane = 0: write plain fp32 instead of the two planes.
 sage_status pack_small_c_image(Context &ctx, const float *img, long long n, long long h, long long w, long long c, long long hp, long long wp,
                                int pad_h, int pad_w, float *hi, long long plane);
 sage_status pack_small_c_filter(Context &ctx, const float *filt, int kh, int kw, int c, int oc, float *hi, long long plane);
@@ -127,6 +128,7 @@ struct TcConv {
     // Element strides between pixels, rows and images; 0 = the dense NHWC ones (c, w * c, h * w * c).  A pixel stride
     // below c makes neighbouring pixels overlap (the C <= 4 layout: 32-float windows 4 * stride floats apart).
     long long sw = 0, sh = 0, sn = 0;
+    bool raw = false;  // `hi` points at plain fp32 (no lo plane): the kernel splits each tile in shared memory
 };
 struct TcGemm {
     TcConv conv;             // when conv.on, `a` is ignored

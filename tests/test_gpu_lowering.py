@@ -237,9 +237,12 @@ def conv64(x, f, stride, pad, dil):
     ((3, 20, 24, 32), (3, 5, 32, 40), (1, 2), (2, 0), (2, 1)),      # unequal window, stride, padding and dilation
     ((2, 40, 40, 96), (7, 7, 96, 32), (2, 2), (3, 3), (1, 1)),      # large window
 ])
-def test_implicit_gemm_convolution(shape, filt, stride, pad, dil):
+@pytest.mark.parametrize("raw", [0, 1])
+def test_implicit_gemm_convolution(monkeypatch, raw, shape, filt, stride, pad, dil):
     """conv_2d with C % 32 == 0 runs as an implicit GEMM: im2col-mode TMA loads from the image's tf32
     planes.  Checked against float64 and against the explicit im2col + GEMM decomposition."""
+    # raw = 1: the opt-in variant that reads the image as plain fp32 and splits each tile inside the SM (measured slower)
+    monkeypatch.setenv("SAGE_CONV_RAW", str(raw))
     rng = np.random.default_rng(sum(shape) + sum(filt))
     x = rng.standard_normal(shape).astype(np.float32)
     f = (rng.standard_normal(filt) / np.sqrt(filt[0] * filt[1] * filt[2])).astype(np.float32)
