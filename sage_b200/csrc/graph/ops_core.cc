@@ -74,6 +74,15 @@ bool is_expand_op(const Operator &op) {
     const ViewOp *v = dynamic_cast<const ViewOp *>(&op);
     return v && v->kind == VExpand;
 }
+// An expand of `in` to `extents` as a bare operator (the evaluator builds these when it moves a map behind an expand).
+std::shared_ptr<Operator> make_expand_op(const TensorDesc &in, const Array &extents) {
+    auto op = std::make_shared<ViewOp>();
+    op->kind = VExpand;
+    op->in = {in};
+    op->out = TensorDesc(in.shape.expand(extents), in.dtype);
+    return op;
+}
+
 // 0 reshape, 1 expand, 2 permute, 3 squeeze, 4 unsqueeze, 5 slice; -1 when `op` is no view
 int view_op_kind(const Operator &op) {
     const ViewOp *v = dynamic_cast<const ViewOp *>(&op);

@@ -96,6 +96,19 @@ const MapExpr *map_expr_of(const Operator &op) {
     return m ? &m->expr : nullptr;
 }
 
+// expand(map(a, b, ..)) == map(expand(a), expand(b), ..): the same elementwise map over operands that are each
+// expanded to `extents`.  Null when `op` is no map with operands.
+std::shared_ptr<Operator> map_over_expanded(const Operator &op, const Array &extents) {
+    const MapOp *m = dynamic_cast<const MapOp *>(&op);
+    if (!m || m->in.empty()) return nullptr;
+    auto f = std::make_shared<MapOp>();
+    f->primitive = false;
+    f->expr = m->expr;
+    for (const TensorDesc &d : m->in) f->in.push_back(TensorDesc(d.shape.expand(extents), d.dtype));
+    f->out = TensorDesc(extents, m->out.dtype);
+    return f;
+}
+
 bool is_copy_map(const Operator &op) {  // organize(): y = x
     const MapOp *m = dynamic_cast<const MapOp *>(&op);
     return m && m->in.size() == 1 && m->expr.kind == MapExpr::Un && m->expr.op == Copy && m->expr.args[0].kind == MapExpr::Input &&

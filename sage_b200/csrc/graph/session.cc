@@ -35,6 +35,9 @@ struct Node {
 
 // ops_map.cc / ops_core.cc / ops_gemm.cc / ops_nn.cc
 bool is_copy_map(const Operator &op);
+std::shared_ptr<Operator> map_over_expanded(const Operator &op, const Array &extents);
+std::shared_ptr<Operator> make_expand_op(const TensorDesc &in, const Array &extents);
+bool is_expand_op(const Operator &op);
 std::string map_expr_text_remap(const MapExpr &e, const std::vector<int> &remap);
 bool is_view_op(const Operator &op);
 bool is_reshape_op(const Operator &op);
@@ -274,8 +277,45 @@ static void lower(Node &n, bool tc, bool softmax_in_gemm, bool attention) {
         }
         return;
     }
+    if (!map_expr_of(*n.op)) return;
+    // An operand that is expand(map(small operands)) — the extended attention mask, (1 - mask) * -1e5 broadcast over
+    // heads and queries — would be a kernel and a tensor of its own.  An elementwise map commutes with expand, so the
+    // small map is moved behind the expand and folded into this map: its operands become broadcast views.
+    if (!is_copy_map(*n.op)) {
+        for (size_t i = 0; i < n.args.size(); ++i) {
+            Node &a = n.args[i];
+            if (a.is_data || a.shared || !is_expand_op(*a.op) || a.args.size() != 1) continue;
+            Node &c = a.args[0];
+            if (c.is_data || c.shared || !map_expr_of(*c.op) || c.args.empty() || c.op->out.shape.size() * 16 > a.op->out.shape.size()) continue;
+            const Array ext = a.op->out.shape.extents;
+            std::shared_ptr<Operator> moved;
+            try {
+                moved = map_over_expanded(*c.op, ext);
+            } catch (const ShapeError &) {
+                moved = nullptr;
+            }
+            if (!moved) continue;
+            std::shared_ptr<Operator> f = fuse_ops(*n.op, *moved, (int)i);
+            if (!f) continue;
+            std::vector<Node> args;
+            for (size_t j = 0; j < n.args.size(); ++j) {
+                if (j != i) {
+                    args.push_back(std::move(n.args[j]));
+                    continue;
+                }
+                for (size_t q = 0; q < c.args.size(); ++q) {  // each operand of the small map, expanded
+                    Node e;
+                    e.op = make_expand_op(c.op->in[q], ext);
+                    e.args.push_back(std::move(c.args[q]));
+                    args.push_back(std::move(e));
+                }
+            }
+            n.op = f;
+            n.args = std::move(args);
+            i = (size_t)-1;  // operands moved: look again from the start
+        }
+    }
     const MapExpr *expr = map_expr_of(*n.op);
-    if (!expr) return;
     if (is_copy_map(*n.op)) {  // a permuted copy of a product
         Node *p = &n.args[0];
         while (!p->is_data && is_view_op(*p->op)) p = &p->args[0];

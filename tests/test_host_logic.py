@@ -264,14 +264,15 @@ def test_bert_base_plan():
     # from the kernel that produces it (GEMM epilogue, attention, layer norm).
     assert t.count("split_tf32") == 72 and t.count("gemm_tc_3xtf32") == 48
     # bias / residual / relu / scale+mask maps and the head split / merge copies are folded into the
-    # GEMMs; what is left is the embedding sum, the per-layer mask bias and the classifier's two maps
-    assert t.count("sage_map") == 1 + 12 + 2
+    # GEMMs, the extended mask (1 - mask) * -1e5 into the attention kernel's expression (an elementwise map
+    # commutes with the expand that follows it); what is left is the embedding sum and the classifier's two maps
+    assert t.count("sage_map") == 1 + 2
     d = c.describe()
     # the three projections of a layer input are one grouped launch, read back as three slabs;
     # "=planes": the only reader is a GEMM, so the fp32 result is not stored at all
     assert d.count("slab(gemm_grouped=planes(") == 36
     # scale + mask is the expression between the score product and the softmax; head merge = the store pattern
-    assert d.count("attention{((x0 / sg_lit(0x41000000u)) + x1)}[store]=planes") == 12
+    assert d.count("attention{((x0 / sg_lit(0x41000000u)) + (((-x1) + sg_lit(0x3f800000u)) * sg_lit(0xc7c35000u)))}[store]=planes") == 12
     assert d.count("gemm{(((float)((x0 + x1) > sg_lit(0x00000000u))) * (x0 + x1))}=planes") == 12  # FFN up: bias + relu
     assert d.count("gemm{((x0 + x1) + x2)}") == 24                           # output / FFN down: bias + residual
     assert d.count("softmax") == 0 and d.count("layer_norm+planes") == 24  # layer norm also feeds the residual
@@ -284,7 +285,7 @@ def test_bert_base_plan():
     c9.eval(m9.pass_(c9.var(np.zeros((32, 128), np.uint32)), c9.var(np.ones((32, 128), np.float32))))
     t9, d9 = c9.trace(), c9.describe()
     assert t9.count("softmax_rows") == 1 and "attention_tc_3xtf32" not in t9 and t9.count("gemm_tc_3xtf32") == 6
-    assert "gemm_batched[store]=planes" in d9 and "gemm_batched{((x0 / sg_lit(0x41000000u)) + x1)}" in d9 and "softmax=planes" in d9
+    assert "gemm_batched[store]=planes" in d9 and "gemm_batched{((x0 / sg_lit(0x41000000u)) + (((-x1) + sg_lit(" in d9 and "softmax=planes" in d9
     c9.close()
     # pattern_fusion bit 1: the softmax moves into the scores GEMM's epilogue (L = 128 keys fit one tile)
     c3 = S.Context(-1, pattern_fusion=3)
