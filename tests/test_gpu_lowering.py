@@ -266,6 +266,43 @@ def test_implicit_gemm_convolution(monkeypatch, raw, shape, filt, stride, pad, d
         plain.close()
 
 
+@pytest.mark.parametrize("shape,filt,pad", [
+    ((3, 56, 56, 64), (3, 3, 64, 64), (1, 1)),      # ResNet-18 layer 1: two output rows of 58 positions per CTA
+    ((5, 28, 28, 128), (3, 3, 128, 128), (1, 1)),   # layer 2: four rows per CTA, 7 CTA tiles per image (pairs span images)
+    ((2, 13, 50, 32), (3, 3, 32, 64), (1, 1)),      # odd height: the last tile of an image is partly outside it
+    ((3, 9, 30, 64), (3, 3, 64, 96), (0, 0)),       # no padding; output channels short of the tile width
+    ((2, 20, 36, 32), (2, 4, 32, 32), (1, 2)),      # even window, unequal padding
+    ((1, 24, 60, 32), (3, 3, 32, 64), (1, 1)),      # the widest rows that fit: a window of 248 pixel rows
+])
+@pytest.mark.parametrize("halo", [1, 0])
+def test_convolution_with_tap_reuse(monkeypatch, halo, shape, filt, pad):
+    """A stride-1 convolution with few output channels loads each CTA's input window once per 32 channels and
+    reads all taps out of it (SAGE_CONV_HALO=0: one im2col load per tap).  With a bias, a residual and relu in
+    the epilogue, against float64 and the explicit decomposition."""
+    monkeypatch.setenv("SAGE_CONV_HALO", str(halo))
+    rng = np.random.default_rng(sum(shape) + sum(filt) + 7)
+    x = rng.standard_normal(shape).astype(np.float32)
+    f = (rng.standard_normal(filt) / np.sqrt(filt[0] * filt[1] * filt[2])).astype(np.float32)
+    b = rng.standard_normal(filt[3]).astype(np.float32)
+    conv = conv64(x, f, (1, 1), pad, (1, 1))
+    r = rng.standard_normal(conv.shape).astype(np.float32)
+    ref = np.maximum(conv + b + r, 0)
+    lowered, plain = S.Context(0), S.Context(0, pattern_fusion=0)
+    try:
+        outs = []
+        for ctx in (lowered, plain):
+            y = S.relu(S.conv_2d(ctx.var(x), ctx.var(f), [1, 1], list(pad), [1, 1]) + ctx.var(b) + ctx.var(r))
+            outs.append(y.eval(ctx))
+        assert "<implicit conv>" in lowered.describe()
+        assert outs[0].shape == ref.shape
+        assert gemm_err(outs[0], ref) <= 1e-4 and gemm_err(outs[1], ref) <= 1e-4
+        assert gemm_err(outs[0], outs[1]) <= 1e-5
+        assert lowered.status_word() == 0
+    finally:
+        lowered.close()
+        plain.close()
+
+
 @pytest.mark.parametrize("b,lq,lk,d", [(6, 128, 128, 64), (5, 70, 96, 32), (3, 300, 200, 64), (4, 64, 256, 32), (2, 130, 33, 64)])
 def test_row_softmax_in_the_gemm_epilogue(b, lq, lk, d):
     """softmax(q k^T * scale + mask) with the keys of a row inside one tile (L_k <= 256) can be computed by
