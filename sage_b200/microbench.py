@@ -49,17 +49,19 @@ def timed(ctx, fn, reps, names):
 
 def case_gemm(ctx, a):
     m, n, k, b = a.m, a.n, a.k, a.batch
-    A, B, C = ctx.tensor(np.random.default_rng(0).uniform(-1, 1, (b, m, k)).astype(np.float32)), \
-        ctx.tensor(np.random.default_rng(1).uniform(-1, 1, (b, k, n)).astype(np.float32)), ctx.empty((b, m, n))
+    ta, tb = int(getattr(a, "ta", 0)), int(getattr(a, "tb", 0))  # 1: the operand is stored transposed ([k, m] / [n, k])
+    A = ctx.tensor(np.random.default_rng(0).uniform(-1, 1, (b, k, m) if ta else (b, m, k)).astype(np.float32))
+    B = ctx.tensor(np.random.default_rng(1).uniform(-1, 1, (b, n, k) if tb else (b, k, n)).astype(np.float32))
+    C = ctx.empty((b, m, n))
 
     def go():
-        ctx._ck(S.lib.sage_gemm_strided_batched(ctx.h, 0, 0, L(m), L(n), L(k), A.buf, L(0), L(k), L(m * k), B.buf, L(0), L(n), L(k * n),
+        ctx._ck(S.lib.sage_gemm_strided_batched(ctx.h, ta, tb, L(m), L(n), L(k), A.buf, L(0), L(m if ta else k), L(m * k), B.buf, L(0), L(k if tb else n), L(k * n),
                                                 C.buf, L(0), L(n), L(m * n), L(b)))
     ms, prof = timed(ctx, go, a.reps, ["gemm", "reduce"])  # "reduce": the sum over K slices when the product is split over K
     split_ms = prof.get("split_tf32", (0, 0.0))[1] / a.reps
     hbm, bf16, src = peaks()
     tf = 2.0 * m * n * k * b / (ms * 1e-3) / 1e12
-    return {"case": "gemm", "m": m, "n": n, "k": k, "batch": b, "us": 1e3 * ms, "split_us": 1e3 * split_ms, "tflops_f32_equivalent": tf,
+    return {"case": "gemm", "m": m, "n": n, "k": k, "batch": b, "ta": ta, "tb": tb, "us": 1e3 * ms, "split_us": 1e3 * split_ms, "tflops_f32_equivalent": tf,
             "tensor_pipe_tflops": 3 * tf, "peak_bf16_tflops": bf16, "frac_of_bf16_peak": 3 * tf / bf16,
             "note": "3xTF32: 3 tensor-core MMAs per logical product; TF32 runs at half the bf16 rate, so 1.0 here would be frac 0.5",
             "peak_source": src, "kernel": [k_ for k_ in prof if k_.startswith("gemm")][0]}
@@ -310,6 +312,8 @@ def main():
     ap.add_argument("--n", type=int, default=768)
     ap.add_argument("--k", type=int, default=768)
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--ta", type=int, default=0, help="gemm: operand A is stored as [k, m]")
+    ap.add_argument("--tb", type=int, default=0, help="gemm: operand B is stored as [n, k]")
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=4096)
     ap.add_argument("--reps", type=int, default=20)
