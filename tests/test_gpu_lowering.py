@@ -273,6 +273,8 @@ def test_implicit_gemm_convolution(monkeypatch, raw, shape, filt, stride, pad, d
     ((3, 9, 30, 64), (3, 3, 64, 96), (0, 0)),       # no padding; output channels short of the tile width
     ((2, 20, 36, 32), (2, 4, 32, 32), (1, 2)),      # even window, unequal padding
     ((1, 24, 60, 32), (3, 3, 32, 64), (1, 1)),      # the widest rows that fit: a window of 248 pixel rows
+    ((9, 3, 40, 32), (3, 3, 32, 32), (1, 1)),       # an image is lower than a CTA tile: one tile per image, pairs span images
+    ((3, 16, 40, 64), (1, 3, 64, 64), (0, 1)),      # a single filter row: the window has no extra rows
 ])
 @pytest.mark.parametrize("halo", [1, 0])
 def test_convolution_with_tap_reuse(monkeypatch, halo, shape, filt, pad):
