@@ -753,6 +753,41 @@ def test_program_cache_and_allocator_reuse(ctx):
     assert ctx.status_word() == 0
 
 
+@pytest.mark.parametrize("m,n,k,batch", [(4096, 3072, 768, 1), (4096, 3072, 96, 1), (2048, 1500, 160, 1), (1024, 1216, 64, 6), (3000, 1100, 100, 1)])
+def test_gemm_with_ragged_column_tiles(ctx, monkeypatch, m, n, k, batch):
+    """A launch of 256-wide tiles whose last wave would be badly filled ends each row block with 192-wide tiles instead
+    (4096 x 3072: nine 256-wide and four 192-wide column tiles).  A narrow tile runs the same code with a smaller N in its
+    MMAs, so every element is computed exactly as with uniform tiles: equal bits with SAGE_GEMM_RAGGED=0; also against
+    float64, and with the bias + relu epilogue and transposed operands."""
+    rng = np.random.default_rng(77 + n + k)
+    a = rng.uniform(-1, 1, (batch, m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (batch, k, n)).astype(np.float32)
+    bias = rng.standard_normal((n,)).astype(np.float32)
+    f64 = a.astype(np.float64) @ b.astype(np.float64)
+    va, vb, vbias = ctx.var(a), ctx.var(b), ctx.var(bias)
+    vbt = ctx.var(np.ascontiguousarray(b.transpose(0, 2, 1)))  # the same B stored [n, k]
+    outs = {}
+    for ragged in ("1", "0"):
+        monkeypatch.setenv("SAGE_GEMM_RAGGED", ragged)  # read at every launch
+        ctx.clear()
+        y = S.matmul_batched(va, vb) if batch > 1 else S.matmul(va.view([m, k]), vb.view([k, n]))
+        plain = y.eval(ctx).reshape(batch, m, n)
+        fused = None
+        if batch == 1:
+            fused = S.relu(S.matmul(va.view([m, k]), vb.view([k, n])) + vbias).eval(ctx)
+            tb = S.gemm(va.view([m, k]), vbt.view([n, k]), False, True).eval(ctx)
+            assert np.array_equal(tb, plain[0])
+        outs[ragged] = (plain, fused)
+    assert np.array_equal(outs["1"][0], outs["0"][0])
+    assert gemm_err(outs["1"][0], f64) <= 1e-4
+    assert np.linalg.norm(outs["1"][0] - f64) / np.linalg.norm(f64) <= 2e-6
+    if batch == 1:
+        assert np.array_equal(outs["1"][1], outs["0"][1])
+        assert gemm_err(outs["1"][1], np.maximum(f64[0] + bias, 0)) <= 1e-4
+    assert ctx.status_word() == 0
+    ctx.clear()
+
+
 @pytest.mark.parametrize("m,n,k,batch", [(4096, 768, 768, 1), (4096, 3072, 768, 1), (4096, 768, 3072, 1), (128, 25600, 512, 1), (512, 640, 1024, 5),
                                          (300, 1000, 2100, 1), (4096, 768, 200, 1)])
 def test_gemm_shapes_whose_tiles_are_shared_between_ctas(ctx, monkeypatch, m, n, k, batch):
