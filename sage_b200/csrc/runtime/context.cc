@@ -150,6 +150,8 @@ Context::~Context() {
             if (kv.second->cu_module && driver().ModuleUnload) driver().ModuleUnload(kv.second->cu_module);
         if (streamk_block) alloc_->free(streamk_block);
         streamk_block = nullptr;
+        if (gemm_trace_block) alloc_->free(gemm_trace_block);
+        gemm_trace_block = nullptr;
         alloc_.reset();
         if (status_word_dev) cudaFree(status_word_dev);
         cudaStreamDestroy(stream_);

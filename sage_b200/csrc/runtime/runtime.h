@@ -163,6 +163,7 @@ public:
     // Scratch of the stream-K GEMM (partial accumulators of tiles shared between CTAs + their hand-over flags), taken
     // from the pool on first use and kept; `streamk_epoch` is the value the flags of the next launch are raised to.
     Block *streamk_block = nullptr;
+    Block *gemm_trace_block = nullptr;  // per-CTA cycle counters of a GEMM launch run with SAGE_GEMM_TRACE (sm_count x 16 words)
     size_t streamk_bytes = 0;
     uint32_t streamk_epoch = 0;
     // Set by the evaluator around one operator's compute(): a tensor-core GEMM will read the result,

@@ -67,6 +67,63 @@ def case_gemm(ctx, a):
             "peak_source": src, "kernel": [k_ for k_ in prof if k_.startswith("gemm")][0]}
 
 
+def case_gemm_trace(ctx, a):
+    """Where the cycles of one tensor-core GEMM launch go, counted inside the kernel (SAGE_GEMM_TRACE: the launch runs
+    the instrumented build and the host reads 16 words per CTA; see TcParams::trace).  Cycles become microseconds with
+    the launch's own clock: cycles of the longest CTA / its global-timer duration."""
+    import struct
+    import tempfile
+    m, n, k, b = a.m, a.n, a.k, a.batch
+    A = ctx.tensor(np.random.default_rng(0).uniform(-1, 1, (b, m, k)).astype(np.float32))
+    B = ctx.tensor(np.random.default_rng(1).uniform(-1, 1, (b, k, n)).astype(np.float32))
+    C = ctx.empty((b, m, n))
+
+    def go():
+        ctx._ck(S.lib.sage_gemm_strided_batched(ctx.h, 0, 0, L(m), L(n), L(k), A.buf, L(0), L(k), L(m * k), B.buf, L(0), L(n), L(k * n),
+                                                C.buf, L(0), L(n), L(m * n), L(b)))
+    for _ in range(3):
+        go()
+    ctx.sync()
+    path = tempfile.mktemp(suffix=".gemm_trace")
+    os.environ["SAGE_GEMM_TRACE"] = path
+    try:
+        for _ in range(3):
+            go()
+        ctx.sync()
+    finally:
+        del os.environ["SAGE_GEMM_TRACE"]
+    raw = open(path, "rb").read()
+    os.unlink(path)
+    recs, at = [], 0
+    while at < len(raw):
+        hdr = struct.unpack("8i", raw[at:at + 32])
+        at += 32
+        grid = hdr[6]
+        recs.append((hdr, np.frombuffer(raw[at:at + grid * 128], dtype=np.uint64).reshape(grid, 16).astype(np.int64)))
+        at += grid * 128
+    hdr, t = recs[-1]
+    ctas = hdr[5]
+    lead = t[::ctas]                      # the CTAs that issue the MMAs
+    ns = (t[:, 1].max() - t[:, 0].min())  # the launch, by the global timer
+    cyc_per_us = float((t[:, 15] / np.maximum(t[:, 1] - t[:, 0], 1)).mean() * 1e3)
+
+    def us(c):
+        return float(np.mean(c)) / cyc_per_us
+    kb = lead[:, 9]
+    span = lead[:, 8] - lead[:, 7]
+    return {"case": "gemm_trace", "m": m, "n": n, "k": k, "batch": b, "bn": hdr[4], "ctas_per_tile": ctas, "grid": hdr[6], "stages": hdr[7],
+            "launch_us": ns / 1e3, "sm_mhz_during_launch": cyc_per_us,
+            "k_blocks_per_leader": [int(kb.min()), int(kb.max())],
+            "cycles_per_k_block": float(span.mean() / max(kb.mean(), 1)),
+            "mma_cycles_per_k_block_at_the_nominal_rate": 3 * 4 * (128 * hdr[4] * 8) // 2048,
+            "issue_cycles_of_12_mmas": {"first_k_block": float(lead[:, 10].mean()), "k_block_41": float(lead[:, 11][lead[:, 11] > 0].mean()) if (lead[:, 11] > 0).any() else None},
+            "us": {"barriers_and_tmem_ready": us(t[:, 2]), "first_load_issued": us(t[:, 4]), "first_mma": us(lead[:, 7]),
+                   "last_commit": us(lead[:, 8]), "cta_end_mean": us(t[:, 15]), "cta_end_max": float(t[:, 15].max()) / cyc_per_us,
+                   "mma_warp_waited_for_operands": us(lead[:, 5]), "mma_warp_waited_for_tmem": us(lead[:, 6]),
+                   "tma_waited_for_a_free_stage": us(t[:, 3]), "epilogue_waited_for_accumulators": us(t[:, 12]),
+                   "epilogue_stores": us(t[:, 13]), "store_per_tile": float(t[:, 13].sum()) / max(float(t[:, 14].sum()), 1.0) / cyc_per_us}}
+
+
 def row_case(ctx, a, kind):
     rows, cols = a.rows, a.cols
     x = ctx.var(np.random.default_rng(2).standard_normal((rows, cols), dtype=np.float32))
@@ -338,6 +395,8 @@ def main():
     for c in cases:
         if c == "gemm":
             r = case_gemm(ctx, a)
+        elif c == "gemm_trace":
+            r = case_gemm_trace(ctx, a)
         elif c == "config1":
             r = case_config1(ctx, a)
         elif c == "train_resnet":
