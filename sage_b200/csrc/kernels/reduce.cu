@@ -214,75 +214,166 @@ static RDims canonical_inner(const Dims &in) {
 }
 
 // Column reduction: x is [rows, cols] with unit column stride and `pitch` elements between rows; y[c]
-// combines x[r, c] over the rows of this block's chunk (blockIdx.y).  A warp reads 32 * VEC consecutive
-// columns of a row (128 or, with 16-byte loads, 512 contiguous bytes); the 8 warps of a block take rows 8
-// apart, four rows in flight each.  With more than one chunk the partial results go to scratch [chunks, cols] and a second launch
-// of the same kernel combines them: the order of combination is fixed, so results repeat bit for bit.
-template <typename T, int VEC>
-__global__ void __launch_bounds__(256) reduce_cols_kernel(const T *__restrict__ x, T *__restrict__ y, long long rows, long long cols,
-                                                          long long pitch, long long rows_per_chunk, int kind, int ref_compat) {
-    grid_dependency_sync();
+// combines x[r, c] over the rows.  A warp reads 32 * VEC consecutive columns of a row (128 or, with 16-byte
+// loads, 512 contiguous bytes); the 8 warps of a block take rows 8 apart, four rows in flight each.  With
+// gridDim.y > 1 the rows are cut into chunks: every block leaves its chunk's result in `partial`
+// [chunks, cols], takes a ticket for its column tile, and the block that draws the last ticket of a tile
+// combines the tile's partial rows the same way.  The order of combination depends on the launch geometry
+// only, so results repeat bit for bit.  `tickets` (one word per column tile) is zero before the launch and
+// is left zero by it.
+template <typename T, int VEC, int U, bool COHERENT>
+__device__ __forceinline__ void reduce_cols_pass(const T *x, long long r0, long long r1, long long pitch, long long col, long long cols,
+                                                 int kind, T (*part)[32 * VEC + 1]) {
     struct alignas(sizeof(T) * VEC) Vec {
         T v[VEC];
     };
-    __shared__ T part[8][32 * VEC + 1];
+    auto load = [](const T *p) {
+        Vec v;
+        if (!COHERENT) {
+            v = *reinterpret_cast<const Vec *>(p);
+        } else if (VEC == 4) {  // written by other blocks of this launch: read through the L2
+            const int4 raw = __ldcg(reinterpret_cast<const int4 *>(p));
+            memcpy(&v, &raw, sizeof(v));
+        } else {
+            const int raw = __ldcg(reinterpret_cast<const int *>(p));
+            memcpy(&v, &raw, sizeof(raw));
+        }
+        return v;
+    };
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const long long col = ((long long)blockIdx.x * 32 + tx) * VEC;  // VEC consecutive columns per lane (cols % VEC == 0)
-    const long long r0 = (long long)blockIdx.y * rows_per_chunk;
-    const long long r1 = r0 + rows_per_chunk < rows ? r0 + rows_per_chunk : rows;
-    T acc[4][VEC];
+    T acc[U][VEC];
 #pragma unroll
-    for (int u = 0; u < 4; ++u)
+    for (int u = 0; u < U; ++u)
 #pragma unroll
         for (int e = 0; e < VEC; ++e) acc[u][e] = Ops<T>::identity(kind);
     if (col < cols) {
         const T *base = x + col;
         long long r = r0 + ty;
-        for (; r + 24 < r1; r += 32) {  // four rows in flight per thread
-            Vec v[4];
+        for (; r + 8 * (U - 1) < r1; r += 8 * U) {  // U rows in flight per thread
+            Vec v[U];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const Vec *>(base + (r + 8 * u) * pitch);
+            for (int u = 0; u < U; ++u) v[u] = load(base + (r + 8 * u) * pitch);
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < U; ++u)
 #pragma unroll
                 for (int e = 0; e < VEC; ++e) acc[u][e] = Ops<T>::apply(kind, acc[u][e], v[u].v[e]);
         }
         for (; r < r1; r += 8) {
-            const Vec v = *reinterpret_cast<const Vec *>(base + r * pitch);
+            const Vec v = load(base + r * pitch);
 #pragma unroll
             for (int e = 0; e < VEC; ++e) acc[0][e] = Ops<T>::apply(kind, acc[0][e], v.v[e]);
         }
     }
 #pragma unroll
-    for (int e = 0; e < VEC; ++e)
-        part[ty][tx * VEC + e] = Ops<T>::apply(kind, Ops<T>::apply(kind, acc[0][e], acc[1][e]), Ops<T>::apply(kind, acc[2][e], acc[3][e]));
-    __syncthreads();
-    // the 8 partial rows are combined in a fixed order; 32 * VEC columns spread over the 256 threads
+    for (int e = 0; e < VEC; ++e) {
+#pragma unroll
+        for (int w = 1; w < U; w *= 2)  // pairwise: (0 1) (2 3) ..., then (01 23) ...
+#pragma unroll
+            for (int u = 0; u + w < U; u += 2 * w) acc[u][e] = Ops<T>::apply(kind, acc[u][e], acc[u + w][e]);
+        part[ty][tx * VEC + e] = acc[0][e];
+    }
+}
+
+// The 8 partial rows in shared memory are combined in a fixed order; 32 * VEC columns spread over the 256 threads.
+template <typename T, int VEC>
+__device__ __forceinline__ void reduce_cols_store(T (*part)[32 * VEC + 1], T *y, long long cols, int kind, int from_zero) {
     for (int c = threadIdx.x; c < 32 * VEC; c += 256) {
         const long long out_col = (long long)blockIdx.x * 32 * VEC + c;
         if (out_col >= cols) continue;
         T a = part[0][c];
 #pragma unroll
         for (int i = 1; i < 8; ++i) a = Ops<T>::apply(kind, a, part[i][c]);
-        if (ref_compat) a = Ops<T>::apply(kind, (T)0, a);
-        y[(long long)blockIdx.y * cols + out_col] = a;
+        if (from_zero) a = Ops<T>::apply(kind, (T)0, a);
+        y[out_col] = a;
     }
+}
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) reduce_cols_kernel(const T *__restrict__ x, T *__restrict__ y, long long rows, long long cols,
+                                                          long long pitch, long long rows_per_chunk, int kind, int ref_compat, T *partial,
+                                                          unsigned *tickets) {
+    grid_dependency_sync();
+    __shared__ T part[8][32 * VEC + 1];
+    __shared__ int last_of_tile;
+    const long long col = ((long long)blockIdx.x * 32 + (threadIdx.x & 31)) * VEC;  // VEC consecutive columns per lane (cols % VEC == 0)
+    const long long r0 = (long long)blockIdx.y * rows_per_chunk;
+    const long long r1 = r0 + rows_per_chunk < rows ? r0 + rows_per_chunk : rows;
+    reduce_cols_pass<T, VEC, 4, false>(x, r0, r1, pitch, col, cols, kind, part);
+    __syncthreads();
+    if (gridDim.y == 1) {
+        reduce_cols_store<T, VEC>(part, y, cols, kind, ref_compat);
+        return;
+    }
+    // the accumulator rule (start from 0) is applied once, by the block that combines the chunks
+    reduce_cols_store<T, VEC>(part, partial + (long long)blockIdx.y * cols, cols, kind, 0);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned drawn = atomicAdd(tickets + blockIdx.x, 1u);
+        last_of_tile = drawn == gridDim.y - 1;
+        if (last_of_tile) tickets[blockIdx.x] = 0;  // every other block of the tile has drawn: nobody reads it again
+    }
+    __syncthreads();
+    if (!last_of_tile) return;
+    __threadfence();
+    reduce_cols_pass<T, VEC, 8, true>(partial, 0, (long long)gridDim.y, cols, col, cols, kind, part);
+    __syncthreads();
+    reduce_cols_store<T, VEC>(part, y, cols, kind, ref_compat);
+}
+
+// Few slices of a long run: y[i] = x[i] (+) x[i + pitch] (+) ... over `slices` < 64 rows (the partial products of a
+// GEMM split over K, [S, m * n] -> [m * n]).  A thread owns four consecutive outputs and keeps up to eight 16-byte
+// loads in flight; the slices are combined in index order, so the result repeats bit for bit.
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_slices_kernel(const T *__restrict__ x, T *__restrict__ y, long long n_out, long long pitch,
+                                                            int slices, int kind, int ref_compat) {
+    grid_dependency_sync();
+    struct alignas(16) V4 {
+        T v[4];
+    };
+    const long long i = ((long long)blockIdx.x * 256 + threadIdx.x) * 4;
+    if (i >= n_out) return;
+    const T *base = x + i;
+    V4 acc = *reinterpret_cast<const V4 *>(base);
+    int s = 1;
+    for (; s + 7 < slices; s += 8) {
+        V4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const V4 *>(base + (long long)(s + u) * pitch);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc.v[e] = Ops<T>::apply(kind, acc.v[e], v[u].v[e]);
+    }
+    for (; s < slices; ++s) {
+        const V4 v = *reinterpret_cast<const V4 *>(base + (long long)s * pitch);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc.v[e] = Ops<T>::apply(kind, acc.v[e], v.v[e]);
+    }
+    if (ref_compat) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc.v[e] = Ops<T>::apply(kind, (T)0, acc.v[e]);
+    }
+    *reinterpret_cast<V4 *>(y + i) = acc;
 }
 
 template <typename T>
 static sage_status launch_reduce_cols(Context &ctx, int kind, const T *x, long long rows, long long cols, long long pitch, T *y, int compat_in) {
     const int compat = compat_in < 0 ? ctx.opts().ref_compat : compat_in;
-    // 16-byte loads (4 columns per lane) when the rows allow; the second stage reads scratch with pitch = cols
+    // 16-byte loads (4 columns per lane) when the rows allow; the partial rows are read with pitch = cols
     const bool vec = cols % 4 == 0 && pitch % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && cols >= 256;
     const long long tiles = vec ? (cols + 127) / 128 : (cols + 31) / 32;
     auto kernel = vec ? reduce_cols_kernel<T, 4> : reduce_cols_kernel<T, 1>;
+    // two blocks per SM, at least 64 rows each (measured: more and smaller chunks are slower, [4096, 3072] 9.3 -> 13.9 us
+    // with eight blocks per SM, because the block that combines a tile's partial rows then has more of them to read)
     long long chunks = (2LL * ctx.sm_count + tiles - 1) / tiles;
     chunks = std::max(1LL, std::min(chunks, rows / 64));
+    if (tiles > Context::kTickets) chunks = 1;  // so many column tiles fill the machine without cutting the rows
     ctx.note_launch("reduce_cols");
-    if (chunks > 1) ctx.note_launch("reduce_cols");
     if (ctx.dry()) return SAGE_OK;
     if (chunks == 1) {
-        launch_dependent(ctx.pdl, ctx.stream(), kernel, dim3((unsigned)tiles, 1), dim3(256), 0, x, y, rows, cols, pitch, rows, kind, compat);
+        launch_dependent(ctx.pdl, ctx.stream(), kernel, dim3((unsigned)tiles, 1), dim3(256), 0, x, y, rows, cols, pitch, rows, kind, compat,
+                         (T *)nullptr, (unsigned *)nullptr);
         return ctx.check_cuda(cudaGetLastError(), "reduce_cols launch");
     }
     const long long per = (rows + chunks - 1) / chunks;
@@ -290,13 +381,10 @@ static sage_status launch_reduce_cols(Context &ctx, int kind, const T *x, long l
     Block *scratch = ctx.allocator().alloc((size_t)(chunks * cols) * sizeof(T));
     if (!scratch) return ctx.fail(SAGE_ERR_OOM, "out of memory for the partial results of a column reduction");
     T *partial = reinterpret_cast<T *>(scratch->ptr);
-    // the accumulator rule (start from 0) is applied once, by the second stage
-    launch_dependent(ctx.pdl, ctx.stream(), kernel, dim3((unsigned)tiles, (unsigned)chunks), dim3(256), 0, x, partial, rows, cols, pitch, per,
-                     kind, 0);
-    launch_dependent(ctx.pdl, ctx.stream(), kernel, dim3((unsigned)tiles, 1), dim3(256), 0, (const T *)partial, y, chunks, cols, cols, chunks,
-                     kind, compat);
+    launch_dependent(ctx.pdl, ctx.stream(), kernel, dim3((unsigned)tiles, (unsigned)chunks), dim3(256), 0, x, y, rows, cols, pitch, per, kind,
+                     compat, partial, ctx.tickets());
     sage_status st = ctx.check_cuda(cudaGetLastError(), "reduce_cols launch");
-    ctx.allocator().free(scratch);  // stream-ordered: reused only by work enqueued after the second stage
+    ctx.allocator().free(scratch);  // stream-ordered: reused only by work enqueued after this launch
     return st;
 }
 
@@ -321,6 +409,16 @@ static sage_status launch_reduce(Context &ctx, int kind, const T *x, const Dims 
     // [rows, cols] -> [cols] (bias gradients, sums over the batch): the kept axis is the contiguous one
     if (outer_in.ndim == 1 && outer_in.str[0] == 1 && inner.ndim == 1 && inner.str[0] >= n_out && n_out >= 2 && n_in >= 64 && n_out <= (1LL << 31))
         return launch_reduce_cols<T>(ctx, kind, x, n_in, n_out, inner.str[0], y, compat_in);
+    // [S, n] -> [n] with few slices S (the partial products of a GEMM split over K)
+    if (outer_in.ndim == 1 && outer_in.str[0] == 1 && inner.ndim == 1 && inner.str[0] >= n_out && n_in >= 2 && n_in < 64 && n_out >= 4096 &&
+        n_out % 4 == 0 && inner.str[0] % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0) {
+        ctx.note_launch("reduce_slices");
+        if (ctx.dry()) return SAGE_OK;
+        const int compat = compat_in < 0 ? ctx.opts().ref_compat : compat_in;
+        launch_dependent(ctx.pdl, ctx.stream(), reduce_slices_kernel<T>, dim3((unsigned)((n_out / 4 + 255) / 256)), dim3(256), 0, x, y, n_out,
+                         inner.str[0], (int)n_in, kind, compat);
+        return ctx.check_cuda(cudaGetLastError(), "reduce_slices launch");
+    }
     // Few outputs, each over a long run (a sum over a whole tensor, the gradient of a scalar parameter): one
     // CTA per output would leave the machine idle.  The run is cut into S equal chunks, a first launch
     // reduces every (output, chunk) pair into scratch [n_out, S], a second one reduces the S partials; the

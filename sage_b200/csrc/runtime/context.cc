@@ -130,8 +130,8 @@ sage_status Context::create(int device, const sage_ctx_opts &opts, Context **out
         cap = (uint64_t)(free_b * 0.9);
     }
     c->alloc_.reset(new Allocator(std::unique_ptr<DeviceMem>(new CudaMem()), cap, opts.use_cache != 0));
-    if (cudaMalloc(&c->status_word_dev, 256) != cudaSuccess) return SAGE_ERR_DEVICE;
-    cudaMemsetAsync(c->status_word_dev, 0, 256, c->stream_);
+    if (cudaMalloc(&c->status_word_dev, 4096) != cudaSuccess) return SAGE_ERR_DEVICE;
+    cudaMemsetAsync(c->status_word_dev, 0, 4096, c->stream_);
     *out = c.release();
     return SAGE_OK;
 }

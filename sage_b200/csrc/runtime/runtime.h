@@ -159,7 +159,11 @@ public:
     std::string profile_end();
 
     void *timer_events[2] = {nullptr, nullptr};  // cudaEvent_t pair of sage_timer_start/stop
-    uint32_t *status_word_dev = nullptr;  // device word kernels OR error bits into
+    uint32_t *status_word_dev = nullptr;  // device word kernels OR error bits into (word 0 of a 4 KiB block)
+    // Ticket counters for kernels whose last block finishes the work of the others (column reductions): zero between
+    // launches, each launch leaves them zero.  Launches of one context are ordered on its stream, so they can share them.
+    static constexpr int kTickets = 960;
+    unsigned *tickets() const { return reinterpret_cast<unsigned *>(status_word_dev) + 64; }
     // Scratch of the stream-K GEMM (partial accumulators of tiles shared between CTAs + their hand-over flags), taken
     // from the pool on first use and kept; `streamk_epoch` is the value the flags of the next launch are raised to.
     Block *streamk_block = nullptr;

@@ -246,7 +246,9 @@ def test_broadcast_and_strided_views(ctx):
     ((64, 1000), [1], True), ((64, 1000), [0], False), ((7, 9, 11, 5), [0, 2], False), ((7, 9, 11, 5), [3, 1], True),
     ((3, 20000), [1], False), ((5000, 3), [0], False), ((2, 3, 4), [0, 1, 2], False), ((1, 1), [1], True),
     ((128, 7, 7, 64), [0, 1, 2], False), ((6272, 100), [0], True), ((40000, 33), [0], False), ((70, 512), [0], False),
-    ((2048, 1536), [0, 1], False), ((2, 300000), [1], True), ((3, 512, 256), [1, 2], False)])  # long runs, few outputs: two stages
+    ((2048, 1536), [0, 1], False), ((2, 300000), [1], True), ((3, 512, 256), [1, 2], False),  # long runs, few outputs: two stages
+    ((4096, 768), [0], False), ((1000, 260), [0], True),      # column sums cut into row chunks, 16-byte loads
+    ((2, 8192), [0], False), ((8, 16384), [0], True), ((11, 4100), [0], False), ((63, 4096), [0], False)])  # few slices of a long run
 @pytest.mark.parametrize("kind", ["sum", "max", "min", "prod"])
 def test_reduce_vs_oracle(ctx, shape, axes, preserve, kind):
     rng = np.random.default_rng(10)
@@ -262,6 +264,21 @@ def test_reduce_vs_oracle(ctx, shape, axes, preserve, kind):
         # a sum of n terms in a different order: bounded by n * eps * sum|x|; compare against that scale
         scale = np.abs(x).sum(axis=tuple(axes), keepdims=preserve).reshape(ref.shape)
         assert np.all(np.abs(got.astype(np.float64) - ref) <= 1e-6 * np.maximum(scale, 1e-30) * max(1, np.log2(n_red)))
+
+
+def test_column_sums_repeat_bit_for_bit(ctx):
+    # The block that draws the last ticket of a column tile combines the chunks' partial rows; the tickets must be
+    # back at zero for the next launch, and the order of combination must not depend on which block came last.
+    rng = np.random.default_rng(110)
+    for shape in ((4096, 768), (6272, 100), (5000, 2304)):
+        x = rng.standard_normal(shape).astype(np.float32)
+        first = ctx.var(x).sum([0], False).eval(ctx)
+        for _ in range(5):
+            assert np.array_equal(ctx.var(x).sum([0], False).eval(ctx), first)
+        assert np.all(np.abs(first - x.astype(np.float64).sum(0)) <= 1e-5 * np.abs(x).sum(0))
+    xi = rng.integers(-1000, 1000, (3000, 520)).astype(np.int32)
+    assert np.array_equal(ctx.var(xi).sum([0], False).eval(ctx), xi.sum(axis=0, dtype=np.int32))
+    assert np.array_equal(ctx.var(xi).max([0], False).eval(ctx), np.maximum(xi.max(axis=0), 0))  # the accumulator starts at 0
 
 
 def test_reduce_int_exact_and_true_identities():
