@@ -37,6 +37,30 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint32_t *__restrict_
     }
 }
 
+// The same when the index does not vary along the last axis and x is contiguous along it (an embedding lookup: the
+// index is a broadcast view, every output row is a row of the table): 16 bytes per thread and one unravelling per
+// 16 bytes, in 32-bit arithmetic (the per-element kernel spends its time in 64-bit divisions: [4096, 768] rows of a
+// table took 16 us).  `chunks_per_row` = ext[last] / 4; the caller has checked alignment and that n / 4 < 2^31.
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint32_t *__restrict__ x, const uint32_t *__restrict__ ind,
+                                                          uint32_t *__restrict__ y, IDims d, int axis, unsigned n_chunks, unsigned chunks_per_row) {
+    grid_dependency_sync();
+    for (unsigned g = blockIdx.x * blockDim.x + threadIdx.x; g < n_chunks; g += gridDim.x * blockDim.x) {
+        unsigned rem = g / chunks_per_row;
+        const unsigned chunk = g - rem * chunks_per_row;
+        long long ind_idx = 0, x_idx = 0;
+#pragma unroll 1
+        for (int i = d.ndim - 2; i >= 0; --i) {
+            const unsigned e = (unsigned)d.ext[i], q = rem / e, c = rem - q * e;
+            rem = q;
+            ind_idx += (long long)c * d.str[i];
+            if (i != axis) x_idx += (long long)c * d.str2[i];
+        }
+        const long long t = ind[ind_idx];
+        const uint4 v = *reinterpret_cast<const uint4 *>(x + x_idx + t * d.str2[axis] + 4u * chunk);
+        *reinterpret_cast<uint4 *>(y + 4ll * g) = v;
+    }
+}
+
 // y[ sum_{i != axis} c_i * y_str[i] + ind[...] * y_str[axis] ] += x[ sum c_i * x_str[i] ]
 // The reference does a plain read-modify-write, which is only defined when no two work-items
 // hit the same output.  atomicAdd gives the same bits in that case (0 + v == v) and the
@@ -93,7 +117,16 @@ sage_status gather(Context &ctx, const uint32_t *x, const long long *x_str, cons
     long long n = ind_dims.size();
     ctx.note_launch("gather");
     if (ctx.dry() || n == 0) return SAGE_OK;
-    launch_dependent(ctx.pdl, ctx.stream(), gather_kernel, dim3(grid_for(ctx, n)), dim3(256), 0, x, ind, y, d, axis, n);
+    const int last = d.ndim - 1;
+    bool rows = last >= 1 && axis != last && d.str[last] == 0 && d.str2[last] == 1 && d.ext[last] % 4 == 0 && n / 4 < (1ll << 31) &&
+                reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0;
+    for (int i = 0; i < last && rows; ++i)
+        if ((d.ext[i] > 1 || i == axis) && d.str2[i] % 4 != 0) rows = false;  // every gathered row starts on a 16-byte boundary
+    if (rows)
+        launch_dependent(ctx.pdl, ctx.stream(), gather_rows_kernel, dim3(grid_for(ctx, n / 4)), dim3(256), 0, x, ind, y, d, axis, (unsigned)(n / 4),
+                         (unsigned)(d.ext[last] / 4));
+    else
+        launch_dependent(ctx.pdl, ctx.stream(), gather_kernel, dim3(grid_for(ctx, n)), dim3(256), 0, x, ind, y, d, axis, n);
     return ctx.check_cuda(cudaGetLastError(), "gather launch");
 }
 

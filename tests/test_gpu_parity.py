@@ -317,6 +317,16 @@ def test_gather_scatter_exact(ctx):
     iv = S.expand(ctx.var(ids).view([33, 1]), [33, 24])
     got = S.gather(ctx.var(w), iv, 0).eval(ctx)
     assert np.array_equal(got, w[ids])
+    # rows that are not a whole number of 16-byte chunks take the per-element kernel; a batched table takes the row kernel
+    w2 = rng.standard_normal((100, 26)).astype(np.float32)
+    assert np.array_equal(S.gather(ctx.var(w2), S.expand(ctx.var(ids).view([33, 1]), [33, 26]), 0).eval(ctx), w2[ids])
+    w3 = rng.standard_normal((5, 100, 32)).astype(np.float32)
+    ids3 = rng.integers(0, 100, (5, 33, 1)).astype(np.uint32)
+    got = S.gather(ctx.var(w3), S.expand(ctx.var(ids3), [5, 33, 32]), 1).eval(ctx)
+    assert np.array_equal(got, np.take_along_axis(w3, np.broadcast_to(ids3, (5, 33, 32)).astype(np.int64), axis=1))
+    big = rng.standard_normal((3000, 768)).astype(np.float32)
+    idb = rng.integers(0, 3000, (4096,)).astype(np.uint32)
+    assert np.array_equal(S.gather(ctx.var(big), S.expand(ctx.var(idb).view([4096, 1]), [4096, 768]), 0).eval(ctx), big[idb])
     # scatter with unique indices is bit-exact with the reference's read-modify-write
     g = rng.standard_normal((50, 1)).astype(np.float32)
     got = S.scatter(ctx.var(g), ctx.var(idx), 1, [50, 64]).eval(ctx)
