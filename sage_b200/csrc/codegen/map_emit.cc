@@ -66,16 +66,13 @@ SG float sg_lit(uint bits) { return __uint_as_float(bits); }
 // hi = x rounded to tf32 (nearest, ties away), lo = x - hi; when the rounding overflows or x is inf / nan,
 // hi is the truncated value and lo what is left of a finite x (the rule of the GEMM's own split pass)
 SG void sg_split_tf32(float x, float *hi, float *lo) {
-  uint hb;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(x));
-  float hf = __uint_as_float(hb);
-  if ((hb & 0x7f800000u) == 0x7f800000u) {
-    hf = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
-    *lo = ((__float_as_uint(x) & 0x7f800000u) != 0x7f800000u) ? x - hf : 0.f;
-  } else {
-    *lo = x - hf;
-  }
+  const uint xb = __float_as_uint(x);
+  const uint hb = (xb + 0x1000u) & 0xffffe000u;  // cvt.rna.tf32.f32 of a finite value, as an add and a mask
+  const bool finite = (xb & 0x7f800000u) != 0x7f800000u;
+  const bool overflow = !finite || (hb & 0x7f800000u) == 0x7f800000u;
+  const float hf = __uint_as_float(overflow ? (xb & 0xffffe000u) : hb);
   *hi = hf;
+  *lo = finite ? x - hf : 0.f;
 }
 )";
 

@@ -475,6 +475,37 @@ def test_matmul_vs_oracle(ctx, m, n, k):
     check_envelope("matmul %dx%dx%d" % (m, n, k), got, lambda: R.matmul(RV(a), RV(b)).eval().numpy(), f64)
 
 
+def test_matmul_operand_split_at_the_edges_of_the_format(ctx):
+    """The tf32 hi / lo split of the operands: values whose rounding to tf32 would overflow are truncated instead,
+    a subnormal stays harmless, a NaN poisons exactly its row, ties round away from zero."""
+    rng = np.random.default_rng(2011)
+    m, n, k = 256, 128, 64
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(0.25, 1, (k, n)).astype(np.float32)
+    a[3, :] = 0.0
+    a[3, 5] = np.float32(3.4028234e38)          # the largest finite value: rounds to infinity in tf32, must not
+    b[5, :] = 0.5
+    a[7, :] = 0.0
+    a[7, 9] = np.float32(1e-41)                 # subnormal
+    a[11, 2] = np.nan
+    a[13, :] = 0.0
+    a[13, 1] = np.frombuffer(np.uint32(0x3f801000).tobytes(), np.float32)[0]   # exactly half way between two tf32 values
+    a[13, 2] = -a[13, 1]
+    b[1, :] = 1.0
+    b[2, :] = 0.5
+    got = S.matmul(ctx.var(a), ctx.var(b)).eval(ctx)
+    f64 = a.astype(np.float64) @ b.astype(np.float64)
+    assert np.all(np.isfinite(got[3])) and np.allclose(got[3], f64[3], rtol=1e-6)
+    assert np.all(np.isfinite(got[7])) and np.all(np.abs(got[7]) <= 2e-41)   # (the tensor core may flush a subnormal operand)
+    assert np.all(np.isnan(got[11]))
+    finite_rows = [r for r in range(m) if r != 11]
+    assert np.all(np.isfinite(got[finite_rows]))
+    assert np.allclose(got[13], f64[13], rtol=1e-6)   # hi + lo carry the value exactly whichever way the tie went
+    rest = [r for r in range(m) if r not in (3, 7, 11, 13)]
+    assert gemm_err(got[rest], f64[rest]) <= 1e-5
+    assert ctx.status_word() == 0
+
+
 @pytest.mark.parametrize("m,n,k", [(200, 136, 72), (320, 72, 4480)])  # the second: few tiles, long K, split over K
 @pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
 def test_gemm_transposes_vs_oracle(ctx, ta, tb, m, n, k):
