@@ -156,9 +156,9 @@ __global__ void __launch_bounds__(256) reduce_vec_kernel(const T *__restrict__ x
         for (int j = 0; j < 4; ++j) a0 = Ops<T>::apply(kind, a0, p0.v[j]);
     }
     T acc = Ops<T>::apply(kind, Ops<T>::apply(kind, a0, a1), Ops<T>::apply(kind, a2, a3));
-    if (G >= 32) {
+    if (G >= 2) {  // lane 0 of a group of G <= 32 lanes only ever takes in lanes of its own group
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) acc = Ops<T>::apply(kind, acc, shfl_down_t(acc, off));
+        for (int off = (G >= 32 ? 16 : G / 2); off > 0; off >>= 1) acc = Ops<T>::apply(kind, acc, shfl_down_t(acc, off));
     }
     if (G == 256) {
         const int warp = threadIdx.x >> 5;
@@ -476,6 +476,13 @@ static sage_status launch_reduce(Context &ctx, int kind, const T *x, const Dims 
     bool vec = G > 1 && inner.ndim == 1 && inner_contig && n_in % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
     for (int i = 0; i < outer.ndim && vec; ++i)
         if (outer.ext[i] > 1 && outer.str[i] % 4 != 0) vec = false;
+    // Many short rows (the row sums of a softmax gradient, [49152, 128]): eight lanes per row, every 16-byte load of a
+    // lane in flight at once, instead of a warp per row with one load per lane.
+    if (vec && G == 32 && n_in <= 512 && n_out >= 64LL * ctx.sm_count) {
+        blocks = (n_out + 31) / 32;
+        launch_dependent(ctx.pdl, ctx.stream(), reduce_vec_kernel<T, 8>, dim3((unsigned)blocks), dim3(threads), 0, x, y, outer, n_out, n_in, kind, compat);
+        return ctx.check_cuda(cudaGetLastError(), "reduce launch");
+    }
     if (vec) {
         if (G == 32)
             launch_dependent(ctx.pdl, ctx.stream(), reduce_vec_kernel<T, 32>, dim3((unsigned)blocks), dim3(threads), 0, x, y, outer, n_out, n_in, kind, compat);

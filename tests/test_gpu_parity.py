@@ -248,7 +248,8 @@ def test_broadcast_and_strided_views(ctx):
     ((128, 7, 7, 64), [0, 1, 2], False), ((6272, 100), [0], True), ((40000, 33), [0], False), ((70, 512), [0], False),
     ((2048, 1536), [0, 1], False), ((2, 300000), [1], True), ((3, 512, 256), [1, 2], False),  # long runs, few outputs: two stages
     ((4096, 768), [0], False), ((1000, 260), [0], True),      # column sums cut into row chunks, 16-byte loads
-    ((2, 8192), [0], False), ((8, 16384), [0], True), ((11, 4100), [0], False), ((63, 4096), [0], False)])  # few slices of a long run
+    ((2, 8192), [0], False), ((8, 16384), [0], True), ((11, 4100), [0], False), ((63, 4096), [0], False),  # few slices of a long run
+    ((20000, 128), [1], False), ((16384, 68), [1], True), ((10000, 512), [1], False)])  # many short rows: eight lanes per row
 @pytest.mark.parametrize("kind", ["sum", "max", "min", "prod"])
 def test_reduce_vs_oracle(ctx, shape, axes, preserve, kind):
     rng = np.random.default_rng(10)
