@@ -142,21 +142,20 @@ __global__ void __launch_bounds__(256) row_warp_kernel(RowParams p) {
             s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
         }
     s = warp_sum(s);
-    if (MODE == ROW_LSE) {
+    if constexpr (MODE == ROW_LSE) {
         if (lane == 0) p.y[row] = logf(s) + m;
-        return;
-    }
-    float4 *yr = reinterpret_cast<float4 *>(p.y + row * p.cols);
+    } else {
 #pragma unroll
-    for (int i = 0; i < V; ++i) {
-        const int c = lane + 32 * i;
-        if (c < chunks) {
-            float4 o;
-            o.x = v[i].x / s;
-            o.y = v[i].y / s;
-            o.z = v[i].z / s;
-            o.w = v[i].w / s;
-            row_store4(p, row * p.cols + 4LL * c, o);
+        for (int i = 0; i < V; ++i) {
+            const int c = lane + 32 * i;
+            if (c < chunks) {
+                float4 o;
+                o.x = v[i].x / s;
+                o.y = v[i].y / s;
+                o.z = v[i].z / s;
+                o.w = v[i].w / s;
+                row_store4(p, row * p.cols + 4LL * c, o);
+            }
         }
     }
 }
@@ -202,7 +201,6 @@ __global__ void __launch_bounds__(256) row_cta_kernel(RowParams p) {
         const float mean = s1 / n;
         const float var = s2 / n - mean * mean;
         const float denom = sqrtf(var + p.eps);
-        float4 *yr = reinterpret_cast<float4 *>(p.y + row * p.cols);
 #pragma unroll
         for (int i = 0; i < V; ++i) {
             const int c = threadIdx.x + 256 * i;
@@ -235,15 +233,14 @@ __global__ void __launch_bounds__(256) row_cta_kernel(RowParams p) {
             s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
         }
     s = block_reduce(s, false, smem);
-    if (MODE == ROW_LSE) {
+    if constexpr (MODE == ROW_LSE) {
         if (threadIdx.x == 0) p.y[row] = logf(s) + m;
-        return;
-    }
-    float4 *yr = reinterpret_cast<float4 *>(p.y + row * p.cols);
+    } else {
 #pragma unroll
-    for (int i = 0; i < V; ++i) {
-        const int c = threadIdx.x + 256 * i;
-        if (c < chunks) row_store4(p, row * p.cols + 4LL * c, make_float4(v[i].x / s, v[i].y / s, v[i].z / s, v[i].w / s));
+        for (int i = 0; i < V; ++i) {
+            const int c = threadIdx.x + 256 * i;
+            if (c < chunks) row_store4(p, row * p.cols + 4LL * c, make_float4(v[i].x / s, v[i].y / s, v[i].z / s, v[i].w / s));
+        }
     }
 }
 
@@ -254,7 +251,6 @@ __global__ void __launch_bounds__(256) row_block_kernel(RowParams p) {
     __shared__ float smem[8];
     const long long row = blockIdx.x;
     const float *xr = p.x + row * p.cols;
-    float *yr = p.y + row * p.cols;
     if (MODE == ROW_LN) {
         float s1 = 0.f, s2 = 0.f;
         for (long long j = threadIdx.x; j < p.cols; j += blockDim.x) {
@@ -279,11 +275,11 @@ __global__ void __launch_bounds__(256) row_block_kernel(RowParams p) {
     float s = 0.f;
     for (long long j = threadIdx.x; j < p.cols; j += blockDim.x) s += expf(xr[j] - m);
     s = block_reduce(s, false, smem);
-    if (MODE == ROW_LSE) {
+    if constexpr (MODE == ROW_LSE) {
         if (threadIdx.x == 0) p.y[row] = logf(s) + m;
-        return;
+    } else {
+        for (long long j = threadIdx.x; j < p.cols; j += blockDim.x) row_store1(p, row * p.cols + j, expf(xr[j] - m) / s);
     }
-    for (long long j = threadIdx.x; j < p.cols; j += blockDim.x) row_store1(p, row * p.cols + j, expf(xr[j] - m) / s);
 }
 
 template <int MODE>
