@@ -444,12 +444,16 @@ def test_bert_training_plan():
         opt.update(grads, c)
         c.clear()
         t = c.trace()
-        counts.append({k: t.count(k) for k in ("sage_row_program", "split_tf32", "gemm_tc_3xtf32", "adam_update", "layernorm_rows")})
+        counts.append({k: t.count(k) for k in ("sage_row_program", "split_tf32", "gemm_tc_3xtf32", "adam_update", "layernorm_rows",
+                                               "reduce_slices", "reduce_cols")})
     first, steady = counts
     # LayerNorm backward (2 per layer + the embedding's) and two softmax backward pieces per layer
     assert steady["sage_row_program"] == first["sage_row_program"] == (2 * layers + 1) + 2 * layers
     assert first["split_tf32"] == 6 * layers and steady["split_tf32"] == 0                              # the weights, once
     assert steady["gemm_tc_3xtf32"] == 24 * layers and steady["layernorm_rows"] == 2 * layers + 1
+    # the six weight gradients of a layer are cut over K and summed by the slice kernel; the six bias gradients are
+    # column sums, one launch each
+    assert steady["reduce_slices"] == 6 * layers and steady["reduce_cols"] == 6 * layers
     d = c.describe()
     assert "row_program[4096x768" in d and "row_program[49152x128" in d
     c.close()
