@@ -125,6 +125,13 @@ public:
     sage_status check_cuda(int err, const char *what);
 
     sage_status module_get(const std::string &src, Module **out);
+    // A launcher whose translation unit is a fixed text behind a few generated lines looks its module up under those
+    // lines alone (hashing and comparing the whole source on every launch costs the host ~10 us per launch).
+    Module *module_find(const std::string &key) const {
+        auto it = module_keys_.find(key);
+        return it == module_keys_.end() ? nullptr : it->second;
+    }
+    void module_remember(const std::string &key, Module *m) { module_keys_[key] = m; }
     // How many blocks of `block_threads` threads and `smem` dynamic bytes of this kernel fit on one SM (>= 1).
     int blocks_per_sm(Module *m, const char *name, int block_threads, uint32_t smem);
     // `dependent`: the kernel begins with griddepcontrol.wait, so it may be launched with programmatic
@@ -185,6 +192,7 @@ private:
     std::shared_ptr<Allocator> alloc_;
     std::string last_error_;
     std::unordered_map<std::string, std::unique_ptr<Module>> modules_;
+    std::unordered_map<std::string, Module *> module_keys_;  // short keys of modules_ entries (which own them)
     std::vector<void *> prof_events_;  // cudaEvent_t pool, reused across profile runs
     std::vector<std::string> prof_names_;
     size_t prof_used_ = 0;
